@@ -1,0 +1,103 @@
+// Shared host/device declarations of libhodu_b200: dtype table, per-device state,
+// error reporting, and the internal launch interfaces of the kernel families.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/hodu_b200.h"
+
+namespace hodu_b200 {
+
+constexpr int kMaxDevices = 16;   // Device::CUDA ids 0..15 (hodu_core tensor/creation.rs:33-37)
+constexpr int kMaxBatchDims = 3;  // collapsed batch dims a tensor-core launch can address
+
+// ------------------------------------------------------------------ dtypes
+__host__ __device__ inline int dtype_size(int dt) {
+  switch (dt) {
+    case HODU_DTYPE_F8E4M3: case HODU_DTYPE_I8: case HODU_DTYPE_U8: case HODU_DTYPE_BOOL:
+    case HODU_DTYPE_F8E5M2: return 1;
+    case HODU_DTYPE_BF16: case HODU_DTYPE_F16: case HODU_DTYPE_I16: case HODU_DTYPE_U16: return 2;
+    case HODU_DTYPE_F32: case HODU_DTYPE_I32: case HODU_DTYPE_U32: return 4;
+    case HODU_DTYPE_F64: case HODU_DTYPE_I64: case HODU_DTYPE_U64: return 8;
+    default: return 0;
+  }
+}
+const char* dtype_name(int dt);
+
+// ------------------------------------------------------------------ errors
+// Records a formatted message for hodu_b200_last_error_message() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+#define HODU_CUDA_TRY(expr, code)                                                       \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return ::hodu_b200::fail((code), "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+// ------------------------------------------------------------------ device state
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t smem_optin = 0;
+  uint32_t* status = nullptr;  // one device word: first bounded wait that gave up
+};
+// Returns the state for `device`, initialising it on first use (thread-safe);
+// nullptr + recorded error on failure.
+DeviceState* device_state(int device);
+// Makes `device` current for the scope, restoring the previous device after.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int device);
+  ~DeviceGuard();
+};
+
+void count_launch(unsigned n = 1);
+void set_last_path(int path);
+int forced_path();
+
+// ------------------------------------------------------------------ problem description
+// One matrix operand of a (batched) product, strides in elements.
+struct Operand {
+  const void* ptr = nullptr;  // base pointer WITHOUT the offset applied
+  int64_t offset = 0;         // elements
+  int64_t stride_r = 0;       // stride of the row index    (M for lhs, K for rhs)
+  int64_t stride_c = 0;       // stride of the column index (K for lhs, N for rhs)
+  int64_t bstride[16] = {0};  // stride per OUTPUT batch dim (0 where broadcast)
+};
+struct Problem {
+  int in_dtype = 0, out_dtype = 0;
+  int64_t M = 0, N = 0, K = 0;
+  int batch_ndim = 0;
+  int64_t batch_shape[16] = {0};
+  int64_t batches = 1;
+  Operand a, b;
+  Operand b2;            // second right-hand operand (SwiGLU up projection)
+  bool swiglu = false;
+  uint32_t swiglu_flags = 0;
+  void* out = nullptr;   // contiguous [batches, M, N]
+  float alpha = 1.0f;    // scale_lhs * scale_rhs
+};
+
+// Generic strided CUDA-core kernel: any layout, every supported dtype pair.
+int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream);
+// tcgen05 kernel. Returns 1 if the layout cannot be described to TMA (nothing
+// launched, `why` says which rule failed), 0 when launched, <0 on error.
+int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// Parsers of the reference's wire formats and the path chooser (api.cu).
+int parse_matmul(const size_t* md, size_t len, Problem* pb);
+int parse_dot(const size_t* md, size_t len, Problem* pb);
+int check_operands(int in_dtype, int out_dtype, const void* lhs, const void* rhs, void* out,
+                   float scale_lhs, float scale_rhs, uint32_t epilogue);
+int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream);
+// Frees the staging memory and streams of the host-buffer forms (host_pipeline.cu).
+void release_host_pipeline(int device);
+// Casts.
+int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, size_t md_len,
+                DeviceState* st, cudaStream_t stream);
+
+}  // namespace hodu_b200

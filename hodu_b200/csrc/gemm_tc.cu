@@ -1,0 +1,735 @@
+// tcgen05 GEMM for sm_100a: C[b] = A[b] . B[b] with the output cast fused into
+// the epilogue.  Replaces the reference's 16x16 shared-memory SIMT kernels
+// `hodu_cuda_matmul_*` / `hodu_cuda_dot_*`
+// (crates/hodu_cuda_kernels/kernels/ops_matrix.cu:9-102,104-165).
+//
+// Shape of one CTA (192 threads, one CTA per SM, persistent over output tiles):
+//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a ring of stages
+//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane)
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator, scale/convert, global store
+// The accumulator tile (128 x BN, f32 or s32) lives in TMEM and is double buffered,
+// so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand layouts: each of A and B may be K-major (K contiguous) or MN-major
+// (M resp. N contiguous); both are described to the tensor core through the
+// shared-memory matrix descriptor, so `B[K,N]` row-major, and the transposed
+// weight view `hodu_nn::Linear` passes, both run without a transposing pre-pass.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out the CTA records a
+// code in the device status word, stops issuing work, drains what it started,
+// frees its TMEM and returns.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace hodu_b200 {
+using namespace ptx;
+
+namespace {
+
+constexpr int BM = 128;                 // tile rows == TMEM lanes
+constexpr int kThreads = 192;
+constexpr int kStageA = BM * 128;       // bytes: 128 rows (or MN elements) x 128 B of K
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, OUT_I8 = 5 };
+
+template <int BN> struct TileCfg {
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStageB = BN * 128;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
+};
+
+struct SmemTail {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+struct TcParams {
+  uint32_t M, N, K;
+  uint32_t tiles_m, tiles_n, num_tiles, k_blocks, group_m;
+  uint32_t bdim1, bdim2;                 // batch = (b0 * bdim1 + b1) * bdim2 + b2
+  uint32_t a_bmul[3], b_bmul[3];         // 0 where the operand broadcasts that batch dim
+  uint32_t a_mn_major, b_mn_major;
+  uint32_t a_boxes, b_boxes;             // TMA boxes per stage
+  uint32_t a_box_bytes, b_box_bytes;
+  uint32_t a_box_mn, b_box_mn;           // M / N elements covered by one box
+  uint32_t bk;                           // K elements per stage (128 bytes worth)
+  uint32_t a_desc_hi, b_desc_hi;         // smem descriptor bits 32..63
+  uint32_t a_desc_lo, b_desc_lo;         // smem descriptor bits 14..31 (leading byte offset)
+  uint32_t a_kstep16, b_kstep16;         // start-address advance per MMA, 16-byte units
+  uint32_t idesc;
+  uint32_t out_vec_ok;                   // rows of `out` allow 16-byte stores
+  uint32_t swiglu_flags;
+  float alpha;
+  unsigned long long ldc, out_batch_stride;  // elements
+  void* out;
+  uint32_t* status;
+};
+
+// -------------------------------------------------------------- bounded waits
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
+                                             volatile uint32_t* abort_flag, uint32_t* status,
+                                             uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 0xFFu) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, code);
+        return false;
+      }
+    }
+  }
+}
+// Used only after an abort: give work already in flight a short time to land.
+__device__ __forceinline__ void wait_drain(uint32_t bar, uint32_t parity) {
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 0xFFu) == 0xFFu && globaltimer_ns() - t0 > 200000000ull) return;
+  }
+}
+
+struct TileCoord {
+  uint32_t batch, mt, nt;
+};
+__device__ __forceinline__ TileCoord decode_tile(const TcParams& p, uint32_t t) {
+  const uint32_t per_batch = p.tiles_m * p.tiles_n;
+  TileCoord c;
+  c.batch = t / per_batch;
+  const uint32_t r = t - c.batch * per_batch;
+  const uint32_t group_sz = p.group_m * p.tiles_n;
+  const uint32_t g = r / group_sz;
+  const uint32_t first_m = g * p.group_m;
+  const uint32_t gm = min(p.tiles_m - first_m, p.group_m);
+  const uint32_t rr = r - g * group_sz;
+  c.mt = first_m + rr % gm;
+  c.nt = rr / gm;
+  return c;
+}
+
+// -------------------------------------------------------------- epilogue helpers
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+template <int OUT> __device__ __forceinline__ float round_to_storage(float x) {
+  if constexpr (OUT == OUT_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  else if constexpr (OUT == OUT_F16) return __half2float(__float2half_rn(x));
+  else return x;
+}
+
+template <int OUT> struct OutBytes {
+  static constexpr int value = (OUT == OUT_F32 || OUT == OUT_I32) ? 4
+                               : (OUT == OUT_BF16 || OUT == OUT_F16) ? 2 : 1;
+};
+
+// Converts 32 values of one output row and stores the first `ncols` of them.
+// `f` holds floats (float accumulators, already scaled) or raw s32 bit patterns.
+template <int OUT>
+__device__ __forceinline__ void store_row_chunk(uint8_t* dst, const uint32_t (&v)[32], int ncols,
+                                                bool vec_ok) {
+  if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
+    if (vec_ok && ncols == 32) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d4[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      uint32_t* d = reinterpret_cast<uint32_t*>(dst);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) d[j] = v[j];
+    }
+  } else if constexpr (OUT == OUT_BF16 || OUT == OUT_F16) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float a = __uint_as_float(v[2 * j]), b = __uint_as_float(v[2 * j + 1]);
+      if constexpr (OUT == OUT_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(a, b);
+        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    if (vec_ok && ncols == 32) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) d4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    } else {
+      uint16_t* d = reinterpret_cast<uint16_t*>(dst);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) d[j] = static_cast<uint16_t>(pk[j >> 1] >> ((j & 1) * 16));
+    }
+  } else {  // one byte per element
+    uint32_t pk[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if constexpr (OUT == OUT_E4M3) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+            make_float2(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1])), __NV_SATFINITE,
+            __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+            make_float2(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])),
+            __NV_SATFINITE, __NV_E4M3);
+        pk[j] = lo | (hi << 16);
+      } else {  // OUT_I8: low 8 bits of the exact s32 sum
+        pk[j] = (v[4 * j] & 0xFFu) | ((v[4 * j + 1] & 0xFFu) << 8) | ((v[4 * j + 2] & 0xFFu) << 16) |
+                ((v[4 * j + 3] & 0xFFu) << 24);
+      }
+    }
+    if (vec_ok && ncols == 32) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      d4[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      d4[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) dst[j] = static_cast<uint8_t>(pk[j >> 2] >> ((j & 3) * 8));
+    }
+  }
+}
+
+// -------------------------------------------------------------- the kernel
+template <int KIND, int BN, int OUT, bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_b2, const TcParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kStageB = Cfg::kStageB;
+  constexpr bool kIntAcc = (KIND == KIND_I8);
+  constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base_u32 - raw_u32);
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + kStages * (kStageA + kStageB));
+  const uint32_t smem_a = base_u32;
+  const uint32_t smem_b = base_u32 + kStages * kStageA;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  volatile uint32_t* abort_flag = &tail->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&tail->full[s]), 1);
+      mbar_init(smem_u32(&tail->empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tail->tmem_full[i]), 1);
+      mbar_init(smem_u32(&tail->tmem_empty[i]), 4);  // one arrive per epilogue warp
+    }
+    mbar_init(smem_u32(&tail->drain), 1);
+    tail->abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    if constexpr (SWIGLU) prefetch_tensormap(&map_b2);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(&tail->tmem_base), Cfg::kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tail->tmem_base);
+
+  const uint32_t code_base = 0x80000000u | ((blockIdx.x & 0xFFFFu) << 4);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint32_t stage_bytes = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
+      uint32_t s = 0, ph = 0, issued = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        const TileCoord tc = decode_tile(p, t);
+        const uint32_t b2 = tc.batch % p.bdim2;
+        const uint32_t tmp = tc.batch / p.bdim2;
+        const uint32_t b1 = tmp % p.bdim1;
+        const uint32_t b0 = tmp / p.bdim1;
+        const int32_t m0 = static_cast<int32_t>(tc.mt * BM);
+        const int32_t n0 = static_cast<int32_t>(tc.nt * kOutCols);
+        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+          ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code_base | 1u);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&tail->full[s]);
+          mbar_arrive_expect_tx(bar, stage_bytes);
+          const int32_t k0 = static_cast<int32_t>(kb * p.bk);
+          uint32_t dst = smem_a + s * kStageA;
+          for (uint32_t i = 0; i < p.a_boxes; ++i, dst += p.a_box_bytes) {
+            const int32_t mn = m0 + static_cast<int32_t>(i * p.a_box_mn);
+            tma_load_5d(dst, &map_a, bar, p.a_mn_major ? mn : k0, p.a_mn_major ? k0 : mn,
+                        b2 * p.a_bmul[2], b1 * p.a_bmul[1], b0 * p.a_bmul[0]);
+          }
+          dst = smem_b + s * kStageB;
+          for (uint32_t i = 0; i < p.b_boxes; ++i, dst += p.b_box_bytes) {
+            const CUtensorMap* mp = &map_b;
+            uint32_t j = i;
+            if constexpr (SWIGLU) {
+              if (i >= p.b_boxes / 2) { mp = &map_b2; j = i - p.b_boxes / 2; }
+            }
+            const int32_t mn = n0 + static_cast<int32_t>(j * p.b_box_mn);
+            tma_load_5d(dst, mp, bar, p.b_mn_major ? mn : k0, p.b_mn_major ? k0 : mn,
+                        b2 * p.b_bmul[2], b1 * p.b_bmul[1], b0 * p.b_bmul[0]);
+          }
+          ++issued;
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (*abort_flag) {
+        // Let copies already issued into this CTA's shared memory land before exit.
+        const uint32_t first = issued > static_cast<uint32_t>(kStages) ? issued - kStages : 0u;
+        for (uint32_t j = first; j < issued; ++j)
+          wait_drain(smem_u32(&tail->full[j % kStages]), (j / kStages) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0, lt = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++lt) {
+        const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
+        ok = wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
+                          code_base | 2u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+          ok = wait_bounded(smem_u32(&tail->full[s]), ph, abort_flag, p.status, code_base | 3u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a16 = (smem_a + s * kStageA) >> 4;
+          const uint32_t b16 = (smem_b + s * kStageB) >> 4;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {
+            const uint64_t adesc =
+                (static_cast<uint64_t>(p.a_desc_hi) << 32) |
+                static_cast<uint64_t>(((a16 + k * p.a_kstep16) & 0x3FFFu) | p.a_desc_lo);
+            const uint64_t bdesc =
+                (static_cast<uint64_t>(p.b_desc_hi) << 32) |
+                static_cast<uint64_t>(((b16 + k * p.b_kstep16) & 0x3FFFu) | p.b_desc_lo);
+            umma<KIND, 1>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0u ? 1u : 0u);
+          }
+          umma_commit_1cta(smem_u32(&tail->empty[s]));  // frees the stage when the MMAs retire
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_1cta(smem_u32(&tail->tmem_full[acc]));
+      }
+      if (*abort_flag) {
+        umma_commit_1cta(smem_u32(&tail->drain));
+        wait_drain(smem_u32(&tail->drain), 0u);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
+    const uint32_t osz = OutBytes<OUT>::value;
+    uint32_t lt = 0;
+    for (uint32_t t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
+      const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
+      bool ok = wait_bounded(smem_u32(&tail->tmem_full[acc]), acc_ph, abort_flag, p.status,
+                             code_base | 4u);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const TileCoord tc = decode_tile(p, t);
+      const uint32_t row = tc.mt * BM + q * 32u + lane;
+      const uint32_t n0 = tc.nt * kOutCols;
+      const bool row_ok = row < p.M;
+      uint8_t* out_row = static_cast<uint8_t*>(p.out) +
+                         (static_cast<unsigned long long>(tc.batch) * p.out_batch_stride +
+                          static_cast<unsigned long long>(row) * p.ldc + n0) * osz;
+      const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
+#pragma unroll 1
+      for (uint32_t c = 0; c < kOutCols / 32; ++c) {
+        const uint32_t col = n0 + c * 32u;
+        if (col >= p.N) break;  // uniform over the warp
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32u, v);
+        if constexpr (SWIGLU) {
+          uint32_t u[32];
+          tmem_ld_32x32(t_row + kOutCols + c * 32u, u);
+          tmem_wait_ld();
+          const bool each = (p.swiglu_flags == HODU_B200_SWIGLU_ROUND_EACH_OP);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float g = __uint_as_float(v[j]), up = __uint_as_float(u[j]);
+            if (each) {
+              g = round_to_storage<OUT>(g);
+              up = round_to_storage<OUT>(up);
+              const float sg = round_to_storage<OUT>(silu_f32(g));
+              v[j] = __float_as_uint(sg * up);
+            } else {
+              v[j] = __float_as_uint(silu_f32(g) * up);
+            }
+          }
+        } else {
+          tmem_wait_ld();
+          if constexpr (!kIntAcc) {
+            if (p.alpha != 1.0f) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
+            }
+          }
+        }
+        if (row_ok) {
+          const int ncols = static_cast<int>(min(32u, p.N - col));
+          store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
+                               p.out_vec_ok != 0u);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tail->tmem_empty[acc]));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// -------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct OperandMap {
+  bool mn_major = false;
+  uint32_t bmul[3] = {0, 0, 0};
+  CUtensorMap map;
+};
+
+struct BatchDims {
+  int n = 0;
+  int64_t size[kMaxBatchDims] = {1, 1, 1};      // outermost first
+  int64_t a_stride[kMaxBatchDims] = {0, 0, 0};
+  int64_t b_stride[kMaxBatchDims] = {0, 0, 0};
+  int64_t b2_stride[kMaxBatchDims] = {0, 0, 0};
+};
+
+// Drops size-1 batch dims and merges neighbours that every operand walks with one stride.
+bool collapse_batch(const Problem& pb, BatchDims* out) {
+  int64_t size[16], as[16], bs[16], b2s[16];
+  int n = 0;
+  for (int d = 0; d < pb.batch_ndim; ++d) {
+    if (pb.batch_shape[d] == 1) continue;
+    size[n] = pb.batch_shape[d];
+    as[n] = pb.a.bstride[d];
+    bs[n] = pb.b.bstride[d];
+    b2s[n] = pb.swiglu ? pb.b2.bstride[d] : 0;
+    ++n;
+  }
+  int m = 0;
+  for (int d = 0; d < n; ++d) {
+    if (m > 0 && as[m - 1] == as[d] * size[d] && bs[m - 1] == bs[d] * size[d] &&
+        b2s[m - 1] == b2s[d] * size[d]) {
+      size[m - 1] *= size[d];
+      as[m - 1] = as[d];
+      bs[m - 1] = bs[d];
+      b2s[m - 1] = b2s[d];
+    } else {
+      size[m] = size[d]; as[m] = as[d]; bs[m] = bs[d]; b2s[m] = b2s[d];
+      ++m;
+    }
+  }
+  if (m > kMaxBatchDims) return false;
+  out->n = m;
+  // right-align into the three slots (slot 2 is the fastest-varying batch dim)
+  for (int d = 0; d < m; ++d) {
+    const int slot = kMaxBatchDims - m + d;
+    out->size[slot] = size[d];
+    out->a_stride[slot] = as[d];
+    out->b_stride[slot] = bs[d];
+    out->b2_stride[slot] = b2s[d];
+  }
+  return true;
+}
+
+inline bool pitch_ok(int64_t s, int esize) {
+  return s > 0 && (s * esize) % 16 == 0 && s * esize < (1ll << 40);
+}
+// Which matrix index of an operand is contiguous.  An operand is K-major when the
+// K index has stride 1 and MN-major when the M (lhs) / N (rhs) index has; the
+// other index must step by a multiple of 16 bytes for TMA.  K-major wins a tie.
+// Returns 0 = K-major, 1 = MN-major, -1 = neither.
+int classify_operand(const Operand& op, int esize, int64_t rows, int64_t cols, bool k_is_col) {
+  const int64_t mn = k_is_col ? rows : cols;
+  const int64_t kk = k_is_col ? cols : rows;
+  const int64_t s_mn = k_is_col ? op.stride_r : op.stride_c;
+  const int64_t s_k = k_is_col ? op.stride_c : op.stride_r;
+  if ((s_k == 1 || kk == 1) && (mn == 1 || pitch_ok(s_mn, esize))) return 0;
+  if ((s_mn == 1 || mn == 1) && (kk == 1 || pitch_ok(s_k, esize))) return 1;
+  return -1;
+}
+
+// Builds the 5-D tensor map {inner, outer, batch2, batch1, batch0} of one operand.
+// rows/cols: logical matrix extents; `k_is_col` says whether K is the column
+// index (lhs) or the row index (rhs).  A K-major box is {128 B of K, tile_mn rows};
+// an MN-major box is {128 B of M/N, 128/esize rows of K} (one stage of K).
+const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_t cols,
+                              bool k_is_col, const BatchDims& bd, const int64_t* bstride,
+                              uint32_t tile_mn /* rows of M/N per K-major box */, OperandMap* out) {
+  const int64_t mn = k_is_col ? rows : cols;
+  const int64_t kk = k_is_col ? cols : rows;
+  const int64_t s_mn = k_is_col ? op.stride_r : op.stride_c;
+  const int64_t s_k = k_is_col ? op.stride_c : op.stride_r;
+  const uintptr_t base = reinterpret_cast<uintptr_t>(op.ptr) + static_cast<uintptr_t>(op.offset) * esize;
+  if (base % 16 != 0) return "operand base address is not 16-byte aligned";
+  if (mn > 0xFFFFFFFFll || kk > 0xFFFFFFFFll) return "extent exceeds 2^32";
+
+  auto stride_ok = [&](int64_t s) { return pitch_ok(s, esize); };
+  const int cls = classify_operand(op, esize, rows, cols, k_is_col);
+  if (cls < 0) return "neither matrix index is contiguous with a 16-byte-multiple pitch";
+  const bool k_major = cls == 0;
+  out->mn_major = !k_major;
+
+  const int64_t inner = k_major ? kk : mn;
+  const int64_t outer = k_major ? mn : kk;
+  int64_t pitch = k_major ? s_mn : s_k;  // elements between consecutive `outer` indices
+  if (outer == 1 || !stride_ok(pitch)) pitch = ((inner * esize + 15) / 16 * 16) / esize;
+  if (!stride_ok(pitch)) return "pitch is not a positive multiple of 16 bytes";
+
+  cuuint64_t dims[5] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), 1, 1, 1};
+  cuuint64_t strides[4];
+  strides[0] = static_cast<cuuint64_t>(pitch) * esize;
+  cuuint64_t natural = strides[0] * dims[1];
+  for (int j = 0; j < 3; ++j) {  // j = 0 is the fastest-varying batch dim (slot 2)
+    const int slot = kMaxBatchDims - 1 - j;
+    const int64_t sz = bd.size[slot], bs = bstride[slot];
+    if (sz > 1 && bs != 0) {
+      if (!stride_ok(bs)) return "batch stride is not a positive multiple of 16 bytes";
+      dims[2 + j] = static_cast<cuuint64_t>(sz);
+      strides[1 + j] = static_cast<cuuint64_t>(bs) * esize;
+      out->bmul[slot] = 1;
+    } else {
+      dims[2 + j] = 1;
+      strides[1 + j] = (natural + 15) / 16 * 16;
+      out->bmul[slot] = 0;
+    }
+    natural = strides[1 + j] * dims[2 + j];
+  }
+  const uint32_t inner_box = 128u / esize;  // 128 bytes: one swizzle row
+  cuuint32_t box[5] = {inner_box, k_major ? tile_mn : inner_box, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                              : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from the driver";
+  const CUresult r = enc(&out->map, dt, 5, reinterpret_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled rejected the layout";
+  return nullptr;
+}
+
+template <int KIND, int BN, int OUT, bool SWIGLU>
+int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+                const TcParams& p, int device, int grid, cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  constexpr size_t smem = Cfg::kStages * (kStageA + Cfg::kStageB) + sizeof(SmemTail) + 1024;
+  static bool attr_set[kMaxDevices] = {false};
+  auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU>;
+  if (!attr_set[device]) {
+    HODU_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)),
+                  HODU_B200_ERR_LAUNCH);
+    attr_set[device] = true;
+  }
+  kern<<<grid, kThreads, smem, stream>>>(ma, mb, mb2, p);
+  HODU_CUDA_TRY(cudaGetLastError(), HODU_B200_ERR_LAUNCH);
+  count_launch();
+  return 0;
+}
+
+template <int KIND, int OUT, bool SWIGLU>
+int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+              const TcParams& p, int device, int grid, cudaStream_t stream) {
+  if constexpr (SWIGLU) {
+    return launch_inst<KIND, 256, OUT, true>(ma, mb, mb2, p, device, grid, stream);
+  } else {
+    switch (bn) {
+      case 256: return launch_inst<KIND, 256, OUT, false>(ma, mb, mb2, p, device, grid, stream);
+      case 128: return launch_inst<KIND, 128, OUT, false>(ma, mb, mb2, p, device, grid, stream);
+      default: return launch_inst<KIND, 64, OUT, false>(ma, mb, mb2, p, device, grid, stream);
+    }
+  }
+}
+
+}  // namespace
+
+int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
+  static const char* none = "";
+  *why = none;
+  int kind, esize, fmt;
+  switch (pb.in_dtype) {
+    case HODU_DTYPE_BF16: kind = KIND_F16; esize = 2; fmt = 1; break;
+    case HODU_DTYPE_F16: kind = KIND_F16; esize = 2; fmt = 0; break;
+    case HODU_DTYPE_F8E4M3: kind = KIND_F8; esize = 1; fmt = 0; break;
+    case HODU_DTYPE_I8: kind = KIND_I8; esize = 1; fmt = 1; break;
+    default: *why = "input dtype has no tensor-core kernel"; return 1;
+  }
+  if (st->cc_major != 10) { *why = "device is not sm_100"; return 1; }
+  if (pb.M < 1 || pb.N < 1 || pb.K < 1 || pb.batches < 1) { *why = "empty problem"; return 1; }
+
+  BatchDims bd;
+  if (!collapse_batch(pb, &bd)) { *why = "more than three independent batch dims"; return 1; }
+  if (pb.batches > 0x7FFFFFFFll) { *why = "too many batches"; return 1; }
+
+  // Tile width: the widest tile that still gives every SM a tile; a tile is never
+  // more than twice as wide as N.  An 8-bit N-contiguous rhs needs >= 128 columns
+  // (one 128-byte swizzle row holds 128 of its elements).
+  const int64_t tiles_m = (pb.M + BM - 1) / BM;
+  const int b_cls = classify_operand(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false);
+  if (b_cls < 0) { *why = "rhs: neither matrix index is contiguous with a 16-byte-multiple pitch"; return 1; }
+  int bn = 256;
+  if (!pb.swiglu) {
+    const int min_bn = (b_cls == 1 && esize == 1) ? 128 : 64;
+    for (int c = 256; c >= min_bn; c >>= 1) {
+      if (c > min_bn && pb.N <= c / 2) continue;
+      bn = c;
+      if (tiles_m * ((pb.N + c - 1) / c) * pb.batches >= st->sm_count) break;
+    }
+  }
+  const int out_cols = pb.swiglu ? bn / 2 : bn;
+  const int64_t tiles_n = (pb.N + out_cols - 1) / out_cols;
+  const int64_t num_tiles = tiles_m * tiles_n * pb.batches;
+  if (num_tiles > 0x7FFFFFFFll) { *why = "too many tiles"; return 1; }
+
+  OperandMap oa, ob, ob2;
+  const char* err = build_operand_map(pb.a, esize, pb.M, pb.K, /*k_is_col=*/true, bd, bd.a_stride, BM, &oa);
+  if (err) { *why = err; return 1; }
+  err = build_operand_map(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false, bd, bd.b_stride,
+                          static_cast<uint32_t>(out_cols), &ob);
+  if (err) { *why = err; return 1; }
+  if (pb.swiglu) {
+    err = build_operand_map(pb.b2, esize, pb.K, pb.N, false, bd, bd.b2_stride,
+                            static_cast<uint32_t>(out_cols), &ob2);
+    if (err) { *why = err; return 1; }
+    if (ob2.mn_major != ob.mn_major) { *why = "gate and up weights differ in layout"; return 1; }
+    for (int j = 0; j < 3; ++j)
+      if (ob2.bmul[j] != ob.bmul[j]) { *why = "gate and up weights differ in batch broadcast"; return 1; }
+  } else {
+    ob2 = ob;
+  }
+
+  TcParams p{};
+  p.M = static_cast<uint32_t>(pb.M); p.N = static_cast<uint32_t>(pb.N); p.K = static_cast<uint32_t>(pb.K);
+  p.tiles_m = static_cast<uint32_t>(tiles_m); p.tiles_n = static_cast<uint32_t>(tiles_n);
+  p.num_tiles = static_cast<uint32_t>(num_tiles);
+  p.bk = 128u / esize;
+  p.k_blocks = static_cast<uint32_t>((pb.K + p.bk - 1) / p.bk);
+  p.group_m = 16;
+  p.bdim1 = static_cast<uint32_t>(bd.size[1]); p.bdim2 = static_cast<uint32_t>(bd.size[2]);
+  for (int j = 0; j < 3; ++j) { p.a_bmul[j] = oa.bmul[j]; p.b_bmul[j] = ob.bmul[j]; }
+  p.a_mn_major = oa.mn_major; p.b_mn_major = ob.mn_major;
+
+  const uint32_t slab_bytes = 128u * p.bk;          // MN-major box: bk rows of 128 bytes
+  const uint32_t mn_per_slab = 128u / esize;
+  const uint32_t kstep_rows = 32u / esize;          // K elements one MMA consumes
+  const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128B swizzle
+  if (oa.mn_major) {
+    p.a_boxes = BM / mn_per_slab; p.a_box_bytes = slab_bytes; p.a_box_mn = mn_per_slab;
+    p.a_desc_lo = (slab_bytes >> 4) << 16; p.a_kstep16 = (kstep_rows * 128u) >> 4;
+  } else {
+    p.a_boxes = 1; p.a_box_bytes = kStageA; p.a_box_mn = BM;
+    p.a_desc_lo = 1u << 16; p.a_kstep16 = 2;
+  }
+  if (ob.mn_major) {
+    p.b_boxes = bn / mn_per_slab; p.b_box_bytes = slab_bytes; p.b_box_mn = mn_per_slab;
+    p.b_desc_lo = (slab_bytes >> 4) << 16; p.b_kstep16 = (kstep_rows * 128u) >> 4;
+  } else {
+    p.b_boxes = pb.swiglu ? 2 : 1; p.b_box_bytes = static_cast<uint32_t>(out_cols) * 128u;
+    p.b_box_mn = static_cast<uint32_t>(out_cols);
+    p.b_desc_lo = 1u << 16; p.b_kstep16 = 2;
+  }
+  p.a_desc_hi = desc_hi; p.b_desc_hi = desc_hi;
+  const uint32_t c_fmt = kind == KIND_I8 ? 2u : 1u;
+  p.idesc = (c_fmt << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+            (static_cast<uint32_t>(oa.mn_major) << 15) | (static_cast<uint32_t>(ob.mn_major) << 16) |
+            (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+  p.alpha = pb.alpha;
+  p.swiglu_flags = pb.swiglu_flags;
+  p.ldc = static_cast<unsigned long long>(pb.N);
+  p.out_batch_stride = static_cast<unsigned long long>(pb.M) * static_cast<unsigned long long>(pb.N);
+  p.out = pb.out;
+  p.status = st->status;
+  const int osz = dtype_size(pb.out_dtype);
+  p.out_vec_ok = (reinterpret_cast<uintptr_t>(pb.out) % 16 == 0 && (pb.N * osz) % 16 == 0 &&
+                  (p.out_batch_stride * osz) % 16 == 0) ? 1u : 0u;
+
+  int device = 0;
+  cudaGetDevice(&device);
+  const int grid = static_cast<int>(num_tiles < st->sm_count ? num_tiles : st->sm_count);
+
+#define HODU_TC(KIND, OUTE, SW) \
+  return launch_bn<KIND, OUTE, SW>(bn, oa.map, ob.map, ob2.map, p, device, grid, stream)
+  if (pb.swiglu) {
+    if (kind != KIND_F16) { *why = "SwiGLU epilogue exists for bf16/f16 only"; return 1; }
+    if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F16, OUT_BF16, true);
+    if (pb.out_dtype == HODU_DTYPE_F16) HODU_TC(KIND_F16, OUT_F16, true);
+    *why = "unsupported SwiGLU output dtype"; return 1;
+  }
+  if (kind == KIND_F16) {
+    if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F16, OUT_BF16, false);
+    if (pb.out_dtype == HODU_DTYPE_F16) HODU_TC(KIND_F16, OUT_F16, false);
+    if (pb.out_dtype == HODU_DTYPE_F32) HODU_TC(KIND_F16, OUT_F32, false);
+  } else if (kind == KIND_F8) {
+    if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F8, OUT_BF16, false);
+    if (pb.out_dtype == HODU_DTYPE_F16) HODU_TC(KIND_F8, OUT_F16, false);
+    if (pb.out_dtype == HODU_DTYPE_F32) HODU_TC(KIND_F8, OUT_F32, false);
+    if (pb.out_dtype == HODU_DTYPE_F8E4M3) HODU_TC(KIND_F8, OUT_E4M3, false);
+  } else {
+    if (pb.out_dtype == HODU_DTYPE_I32) HODU_TC(KIND_I8, OUT_I32, false);
+    if (pb.out_dtype == HODU_DTYPE_I8) HODU_TC(KIND_I8, OUT_I8, false);
+  }
+#undef HODU_TC
+  *why = "output dtype has no tensor-core epilogue";
+  return 1;
+}
+
+}  // namespace hodu_b200

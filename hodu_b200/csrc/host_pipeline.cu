@@ -1,0 +1,192 @@
+// Host-buffer forms of matmul / dot: upload, multiply, download as one pipelined
+// call.  In the reference these are three separate steps, each a full pass:
+// the operands are built on the CPU and copied with `memcpy_stod`
+// (crates/hodu_core/src/be/device.rs:35-55), the product runs
+// (crates/hodu_core/src/be_cuda/storage/ops_matrix.rs:10-93,95-169), and
+// `to_cpu_storage` copies the result back (crates/hodu_core/src/be_cuda/storage.rs:165-173).
+// Here the operands are cut into slices (whole batches, or row blocks of the lhs
+// when there is one matrix) that rotate over a few streams, so the copy engines
+// and the tensor cores overlap; the kernels are the same ones the device forms use.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace hodu_b200 {
+namespace {
+
+constexpr int kSlots = 4;
+
+struct HostPipe {
+  bool ready = false;
+  cudaStream_t stream[kSlots] = {};
+  cudaEvent_t rhs_ready = nullptr;
+  void* buf[3] = {nullptr, nullptr, nullptr};  // lhs, rhs, out staging (grow-only)
+  size_t cap[3] = {0, 0, 0};
+  std::mutex mu;  // one host-form call per device at a time: they share the staging
+};
+HostPipe g_pipe[kMaxDevices];
+
+int ensure(HostPipe* hp, const size_t need[3]) {
+  if (!hp->ready) {
+    for (int i = 0; i < kSlots; ++i)
+      HODU_CUDA_TRY(cudaStreamCreateWithFlags(&hp->stream[i], cudaStreamNonBlocking), HODU_B200_ERR_LAUNCH);
+    HODU_CUDA_TRY(cudaEventCreateWithFlags(&hp->rhs_ready, cudaEventDisableTiming), HODU_B200_ERR_LAUNCH);
+    hp->ready = true;
+  }
+  for (int i = 0; i < 3; ++i) {
+    if (need[i] <= hp->cap[i]) continue;
+    if (hp->buf[i]) {
+      HODU_CUDA_TRY(cudaDeviceSynchronize(), HODU_B200_ERR_LAUNCH);
+      HODU_CUDA_TRY(cudaFree(hp->buf[i]), HODU_B200_ERR_MEMORY);
+      hp->buf[i] = nullptr;
+      hp->cap[i] = 0;
+    }
+    HODU_CUDA_TRY(cudaMalloc(&hp->buf[i], need[i]), HODU_B200_ERR_MEMORY);
+    hp->cap[i] = need[i];
+  }
+  return 0;
+}
+
+bool contiguous_operand(const Problem& pb, const Operand& op, int64_t rows, int64_t cols, int64_t* elems) {
+  // Row-major, offset 0, batch dims densely packed or broadcast as a whole.
+  if (op.offset != 0) return false;
+  if (!((op.stride_c == 1 || cols == 1) && (op.stride_r == cols || rows == 1))) return false;
+  int64_t expect = rows * cols;
+  bool any = false, all = true;
+  for (int d = pb.batch_ndim - 1; d >= 0; --d) {
+    if (pb.batch_shape[d] == 1) continue;
+    if (op.bstride[d] == 0) { all = false; continue; }
+    any = true;
+    if (op.bstride[d] != expect) return false;
+    expect *= pb.batch_shape[d];
+  }
+  if (any && !all) return false;  // partly broadcast: not a fresh tensor's layout
+  *elems = any ? expect : rows * cols;
+  return true;
+}
+
+int host_impl(bool is_dot, int device, int in_dtype, int out_dtype, const void* lhs, const void* rhs,
+              void* out, const size_t* md, size_t len, float sl, float sr) {
+  Problem pb;
+  int r = is_dot ? parse_dot(md, len, &pb) : parse_matmul(md, len, &pb);
+  if (r) return r;
+  r = check_operands(in_dtype, out_dtype, lhs, rhs, out, sl, sr, 0);
+  if (r) return r;
+  if (pb.M == 0 || pb.N == 0 || pb.batches == 0) return 0;
+  if (pb.K == 0) return fail(HODU_B200_ERR_INVALID_INPUT, "host form: K == 0");
+  int64_t a_elems = 0, b_elems = 0;
+  if (!contiguous_operand(pb, pb.a, pb.M, pb.K, &a_elems) || !contiguous_operand(pb, pb.b, pb.K, pb.N, &b_elems))
+    return fail(HODU_B200_ERR_INVALID_INPUT, "host form: operands must be contiguous with offset 0");
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+
+  const int isz = dtype_size(in_dtype), osz = dtype_size(out_dtype);
+  const int64_t c_elems = pb.batches * pb.M * pb.N;
+  HostPipe* hp = &g_pipe[device];
+  std::lock_guard<std::mutex> lock(hp->mu);
+  const size_t need[3] = {static_cast<size_t>(a_elems) * isz, static_cast<size_t>(b_elems) * isz,
+                          static_cast<size_t>(c_elems) * osz};
+  r = ensure(hp, need);
+  if (r) return r;
+
+  pb.in_dtype = in_dtype; pb.out_dtype = out_dtype; pb.alpha = sl * sr;
+  const bool a_batched = a_elems > pb.M * pb.K, b_batched = b_elems > pb.K * pb.N;
+  const uint8_t* hl = static_cast<const uint8_t*>(lhs);
+  const uint8_t* hr = static_cast<const uint8_t*>(rhs);
+  uint8_t* ho = static_cast<uint8_t*>(out);
+  uint8_t* dl = static_cast<uint8_t*>(hp->buf[0]);
+  uint8_t* dr = static_cast<uint8_t*>(hp->buf[1]);
+  uint8_t* dout = static_cast<uint8_t*>(hp->buf[2]);
+
+  if (pb.batches > 1 && a_batched && b_batched) {
+    // Slices of whole batches: both operands of a slice travel with it.
+    const int64_t per = (pb.batches + 4 * kSlots - 1) / (4 * kSlots);
+    int slot = 0;
+    for (int64_t b0 = 0; b0 < pb.batches; b0 += per, slot = (slot + 1) % kSlots) {
+      const int64_t nb = b0 + per <= pb.batches ? per : pb.batches - b0;
+      cudaStream_t s = hp->stream[slot];
+      const size_t ao = static_cast<size_t>(b0) * pb.M * pb.K * isz, bo = static_cast<size_t>(b0) * pb.K * pb.N * isz;
+      const size_t co = static_cast<size_t>(b0) * pb.M * pb.N * osz;
+      HODU_CUDA_TRY(cudaMemcpyAsync(dl + ao, hl + ao, static_cast<size_t>(nb) * pb.M * pb.K * isz, cudaMemcpyHostToDevice, s), HODU_B200_ERR_MEMORY);
+      HODU_CUDA_TRY(cudaMemcpyAsync(dr + bo, hr + bo, static_cast<size_t>(nb) * pb.K * pb.N * isz, cudaMemcpyHostToDevice, s), HODU_B200_ERR_MEMORY);
+      Problem q = pb;
+      q.batch_ndim = 1; q.batch_shape[0] = nb; q.batches = nb;
+      q.a.ptr = dl + ao; q.a.bstride[0] = pb.M * pb.K; q.a.stride_r = pb.K; q.a.stride_c = 1;
+      q.b.ptr = dr + bo; q.b.bstride[0] = pb.K * pb.N; q.b.stride_r = pb.N; q.b.stride_c = 1;
+      q.out = dout + co;
+      r = run_problem(q, st, s);
+      if (r) return r;
+      HODU_CUDA_TRY(cudaMemcpyAsync(ho + co, dout + co, static_cast<size_t>(nb) * pb.M * pb.N * osz, cudaMemcpyDeviceToHost, s), HODU_B200_ERR_MEMORY);
+    }
+  } else if (pb.batches == 1 || (!b_batched && a_batched)) {
+    // One rhs for every row of the (flattened) lhs: upload it once, then stream
+    // row blocks of the lhs through the slots.
+    const int64_t rows = a_batched ? pb.batches * pb.M : pb.M;
+    HODU_CUDA_TRY(cudaMemcpyAsync(dr, hr, static_cast<size_t>(b_elems) * isz, cudaMemcpyHostToDevice, hp->stream[0]), HODU_B200_ERR_MEMORY);
+    HODU_CUDA_TRY(cudaEventRecord(hp->rhs_ready, hp->stream[0]), HODU_B200_ERR_LAUNCH);
+    int64_t per = (rows + 4 * kSlots - 1) / (4 * kSlots);
+    per = (per + 127) / 128 * 128;
+    int slot = 0;
+    for (int64_t r0 = 0; r0 < rows; r0 += per, slot = (slot + 1) % kSlots) {
+      const int64_t nr = r0 + per <= rows ? per : rows - r0;
+      cudaStream_t s = hp->stream[slot];
+      const size_t ao = static_cast<size_t>(r0) * pb.K * isz, co = static_cast<size_t>(r0) * pb.N * osz;
+      HODU_CUDA_TRY(cudaMemcpyAsync(dl + ao, hl + ao, static_cast<size_t>(nr) * pb.K * isz, cudaMemcpyHostToDevice, s), HODU_B200_ERR_MEMORY);
+      HODU_CUDA_TRY(cudaStreamWaitEvent(s, hp->rhs_ready, 0), HODU_B200_ERR_LAUNCH);
+      Problem q = pb;
+      q.batch_ndim = 0; q.batches = 1; q.M = nr;
+      q.a.ptr = dl + ao; q.a.stride_r = pb.K; q.a.stride_c = 1;
+      q.b.ptr = dr; q.b.stride_r = pb.N; q.b.stride_c = 1;
+      q.out = dout + co;
+      r = run_problem(q, st, s);
+      if (r) return r;
+      HODU_CUDA_TRY(cudaMemcpyAsync(ho + co, dout + co, static_cast<size_t>(nr) * pb.N * osz, cudaMemcpyDeviceToHost, s), HODU_B200_ERR_MEMORY);
+    }
+  } else {
+    // Broadcast lhs: no slicing, one pass.
+    cudaStream_t s = hp->stream[0];
+    HODU_CUDA_TRY(cudaMemcpyAsync(dl, hl, static_cast<size_t>(a_elems) * isz, cudaMemcpyHostToDevice, s), HODU_B200_ERR_MEMORY);
+    HODU_CUDA_TRY(cudaMemcpyAsync(dr, hr, static_cast<size_t>(b_elems) * isz, cudaMemcpyHostToDevice, s), HODU_B200_ERR_MEMORY);
+    Problem q = pb;
+    q.a.ptr = dl; q.b.ptr = dr; q.out = dout;
+    r = run_problem(q, st, s);
+    if (r) return r;
+    HODU_CUDA_TRY(cudaMemcpyAsync(ho, dout, static_cast<size_t>(c_elems) * osz, cudaMemcpyDeviceToHost, s), HODU_B200_ERR_MEMORY);
+  }
+  for (int i = 0; i < kSlots; ++i) HODU_CUDA_TRY(cudaStreamSynchronize(hp->stream[i]), HODU_B200_ERR_LAUNCH);
+  return 0;
+}
+
+}  // namespace
+
+void release_host_pipeline(int device) {
+  HostPipe* hp = &g_pipe[device];
+  std::lock_guard<std::mutex> lock(hp->mu);
+  for (int i = 0; i < 3; ++i) {
+    if (hp->buf[i]) cudaFree(hp->buf[i]);
+    hp->buf[i] = nullptr;
+    hp->cap[i] = 0;
+  }
+  if (hp->ready) {
+    for (int i = 0; i < kSlots; ++i) cudaStreamDestroy(hp->stream[i]);
+    cudaEventDestroy(hp->rhs_ready);
+    hp->ready = false;
+  }
+}
+
+}  // namespace hodu_b200
+
+using namespace hodu_b200;
+
+extern "C" {
+int hodu_b200_matmul_host(int device, uint8_t in_dtype, uint8_t out_dtype, const void* lhs, const void* rhs,
+                          void* out, const size_t* md, size_t len, float sl, float sr) {
+  return host_impl(false, device, in_dtype, out_dtype, lhs, rhs, out, md, len, sl, sr);
+}
+int hodu_b200_dot_host(int device, uint8_t in_dtype, uint8_t out_dtype, const void* lhs, const void* rhs,
+                       void* out, const size_t* md, size_t len, float sl, float sr) {
+  return host_impl(true, device, in_dtype, out_dtype, lhs, rhs, out, md, len, sl, sr);
+}
+}

@@ -1,0 +1,57 @@
+"""`hodu_nn::Linear` (crates/hodu_nn/src/modules/linear.rs:38-47) and the SwiGLU MLP
+a caller composes from three of them.  The reference has no SwiGLU module: the
+composition is `down(silu(gate(x)) * up(x))`, five launches and three [M, hidden]
+temporaries there; here gate, up, silu and mul are one kernel."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib, kernels
+from .layout import Layout
+from .op_metadatas import swiglu_metadata
+from .tensor import HoduError, Tensor, _stream
+
+
+class Linear:
+    """weight is [out_features, in_features]; forward = input.matmul(weight.transpose(-2,-1))."""
+
+    def __init__(self, weight: Tensor, bias: Optional[Tensor] = None):
+        if len(weight.shape) != 2:
+            raise HoduError("Linear weight must be 2-D [out, in]")
+        if bias is not None:
+            raise HoduError("bias add is a separate broadcast kernel in the reference and is not on this path")
+        self.weight = weight
+
+    def forward(self, input: Tensor) -> Tensor:
+        return input.matmul(self.weight.transpose(-2, -1))
+
+
+class SwiGluMlp:
+    """Y = down(silu(gate(X)) * up(X)) from three bias-free `Linear` layers."""
+
+    def __init__(self, gate: Linear, up: Linear, down: Linear, rounding: int = _lib.SWIGLU_ROUND_EACH_OP):
+        self.gate, self.up, self.down, self.rounding = gate, up, down, rounding
+
+    def hidden(self, x: Tensor) -> Tensor:
+        """silu(x.gate) * x.up as one launch (`hodu_b200_swiglu`)."""
+        if len(x.shape) != 2:
+            raise HoduError("SwiGluMlp takes a 2-D [tokens, features] input")
+        wg = self.gate.weight.transpose(-2, -1)
+        wu = self.up.weight.transpose(-2, -1)
+        md = swiglu_metadata(x.layout, wg.layout, wu.layout)
+        m, n = x.shape[0], wg.shape[1]
+        out = torch.empty(m * n, dtype=x.storage.dtype, device=x.storage.device)
+        kernels.call_ops_swiglu(x.dtype, x.device_id, x.storage.data_ptr(), wg.storage.data_ptr(),
+                                wu.storage.data_ptr(), out.data_ptr(), md, self.rounding,
+                                _stream(x.storage.device))
+        return Tensor(out, Layout.from_shape((m, n)))
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.down.forward(self.hidden(x))
+
+    def forward_unfused(self, x: Tensor) -> Tensor:
+        """Only the two projections of the reference composition that are GEMMs run through
+        this library; silu and mul are not this library's kernels, so this form is not offered."""
+        raise HoduError("unfused SwiGLU needs the reference's unary/binary kernels, which are outside this path")

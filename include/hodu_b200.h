@@ -1,0 +1,219 @@
+/*
+ * hodu_b200.h -- C ABI of the B200 (sm_100a) matmul / dot / cast path for Hodu.
+ *
+ * This library stands where the reference's `hodu_cuda_kernels` crate stands for
+ * three of its entry points.  Every function below names the reference interface
+ * it replaces (paths are relative to the reference project root).
+ *
+ * Conventions shared by all entry points
+ *  - Return value: 0 on success, otherwise one of the negative HODU_B200_ERR_*
+ *    codes.  Nothing aborts or throws.  The codes mirror the variants of the
+ *    reference's `CudaKernelError` (crates/hodu_cuda_kernels/src/error.rs:7-18).
+ *  - `device` is the CUDA ordinal of `Device::CUDA(n)`
+ *    (crates/hodu_core/src/types/device.rs:4-11).
+ *  - `stream` is a `CUstream`/`cudaStream_t` passed as `void*`; NULL means the
+ *    context's default stream, which is what the reference launches on
+ *    (crates/hodu_cuda_kernels/src/kernels/ops_matrix.rs:572-582).  Work is only
+ *    enqueued: the call returns before the kernel has finished, as in the
+ *    reference.  No implicit synchronisation.
+ *  - dtypes are the `#[repr(u8)]` discriminants of `DType`
+ *    (crates/hodu_core/src/types/dtype.rs:6-30).
+ *  - `metadata` is a HOST array of `size_t` in the wire format built by
+ *    `crates/hodu_core/src/op_metadatas.rs`; strides and offsets are in elements.
+ *    It is read during the call only (no device copy of it is made).
+ *  - The caller owns every buffer.  Inputs may alias each other; `out` must not
+ *    alias an input.  `out` is contiguous, offset 0, and may be uninitialised.
+ *  - Thread-safe: any thread may call for any device.
+ *  - There is no CPU fallback and no cuBLAS: an unsupported dtype or layout is an
+ *    error code.
+ */
+#ifndef HODU_B200_H
+#define HODU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* DType discriminants (crates/hodu_core/src/types/dtype.rs:6-30). */
+enum {
+  HODU_DTYPE_BOOL = 0,
+  HODU_DTYPE_F8E4M3 = 1,
+  HODU_DTYPE_F8E5M2 = 2,
+  HODU_DTYPE_BF16 = 3,
+  HODU_DTYPE_F16 = 4,
+  HODU_DTYPE_F32 = 5,
+  HODU_DTYPE_F64 = 6,
+  HODU_DTYPE_U8 = 7,
+  HODU_DTYPE_U16 = 8,
+  HODU_DTYPE_U32 = 9,
+  HODU_DTYPE_U64 = 10,
+  HODU_DTYPE_I8 = 11,
+  HODU_DTYPE_I16 = 12,
+  HODU_DTYPE_I32 = 13,
+  HODU_DTYPE_I64 = 14
+};
+
+/* Error codes; one per CudaKernelError variant plus a device-status code. */
+enum {
+  HODU_B200_OK = 0,
+  HODU_B200_ERR_INVALID_KERNEL = -1, /* unsupported dtype pair / op          */
+  HODU_B200_ERR_INVALID_INPUT = -2,  /* bad metadata, null pointer, layout   */
+  HODU_B200_ERR_LAUNCH = -3,         /* CUDA launch failed                   */
+  HODU_B200_ERR_MEMORY = -4,         /* allocation or copy failed            */
+  HODU_B200_ERR_DEVICE_STATUS = -5,  /* a kernel reported a bounded wait ran out */
+  HODU_B200_ERR_NOT_INITIALISED = -6
+};
+
+/* Epilogue selector of the *_ex entry points. */
+enum {
+  HODU_B200_EPI_NONE = 0
+};
+
+/* Path selector for hodu_b200_force_path (testing aid). */
+enum {
+  HODU_B200_PATH_AUTO = 0,
+  HODU_B200_PATH_SIMT = 1,   /* generic strided CUDA-core kernel          */
+  HODU_B200_PATH_TENSOR = 2  /* tcgen05 kernel; error if layout unfit     */
+};
+
+/* Flags of hodu_b200_swiglu. */
+enum {
+  /* Round gate/up projections, silu and product to the storage dtype one by one,
+   * as the reference's op-by-op composition does
+   * (Linear::forward -> Tensor::silu -> Tensor::mul, each producing a tensor). */
+  HODU_B200_SWIGLU_ROUND_EACH_OP = 0,
+  /* Keep gate/up/silu in f32 and round the product once. */
+  HODU_B200_SWIGLU_ROUND_ONCE = 1
+};
+
+/*
+ * Per-device set-up: creates the status word and caches device properties.
+ * Replaces the lazily built per-device state of the reference
+ * (`Kernels::new`, crates/hodu_cuda_kernels/src/kernel.rs:102-126, and the
+ * context pool in crates/hodu_core/src/be_cuda/device.rs:20-65).
+ * Called implicitly by the first compute call on a device.
+ */
+int hodu_b200_init(int device);
+void hodu_b200_shutdown(int device);
+
+/*
+ * Batched matmul with broadcasting, output dtype == input dtype.
+ * Replaces `call_ops_matmul`
+ * (crates/hodu_cuda_kernels/src/kernels/ops_matrix.rs:415-429) and the kernels
+ * `hodu_cuda_matmul_{dtype}` (crates/hodu_cuda_kernels/kernels/ops_matrix.cu:9-102).
+ * metadata = [num_els, lhs_ndim, rhs_ndim, batch_ndim, lhs_shape.., rhs_shape..,
+ *             batch_shape.., lhs_strides.., rhs_strides.., lhs_off, rhs_off, M, K, N]
+ * (crates/hodu_core/src/op_metadatas.rs:192-290).
+ * dtypes: f8e4m3, bf16, f16, f32, i8 (i8 keeps the reference CPU semantics: the
+ * exact sum wrapped to 8 bits), i32.
+ */
+int hodu_b200_matmul(int device, void* stream, uint8_t dtype,
+                     const void* lhs, const void* rhs, void* out,
+                     const size_t* metadata, size_t metadata_len);
+
+/*
+ * 2-D matmul.  Replaces `call_ops_dot`
+ * (crates/hodu_cuda_kernels/src/kernels/ops_matrix.rs:611-625) and
+ * `hodu_cuda_dot_{dtype}` (crates/hodu_cuda_kernels/kernels/ops_matrix.cu:104-165).
+ * metadata = [M, K, N, lhs_stride_m, lhs_stride_k, rhs_stride_k, rhs_stride_n,
+ *             lhs_off, rhs_off]  (crates/hodu_core/src/op_metadatas.rs:464-506).
+ */
+int hodu_b200_dot(int device, void* stream, uint8_t dtype,
+                  const void* lhs, const void* rhs, void* out,
+                  const size_t* metadata, size_t metadata_len);
+
+/*
+ * Mixed-dtype forms of the two calls above.  The reference has no such op: its
+ * CUDA dispatch fixes output dtype == input dtype and rejects f8e4m3 / i8
+ * (crates/hodu_core/src/be_cuda/storage/ops_matrix.rs:66-92,142-167).  These carry
+ * what that signature cannot: out = cast_out(scale_lhs * scale_rhs * (lhs . rhs)).
+ * Supported (in -> out): f8e4m3 -> bf16 | f16 | f32 | f8e4m3;  i8 -> i32 | i8;
+ * bf16 -> bf16 | f32;  f16 -> f16 | f32;  f32 -> f32;  i32 -> i32.
+ * Scales apply to floating inputs only and must be 1 for integer inputs.
+ * Float outputs are rounded to nearest even; f8e4m3 output saturates to +-448.
+ */
+int hodu_b200_matmul_ex(int device, void* stream, uint8_t in_dtype, uint8_t out_dtype,
+                        const void* lhs, const void* rhs, void* out,
+                        const size_t* metadata, size_t metadata_len,
+                        float scale_lhs, float scale_rhs, uint32_t epilogue);
+int hodu_b200_dot_ex(int device, void* stream, uint8_t in_dtype, uint8_t out_dtype,
+                     const void* lhs, const void* rhs, void* out,
+                     const size_t* metadata, size_t metadata_len,
+                     float scale_lhs, float scale_rhs, uint32_t epilogue);
+
+/*
+ * Element-wise dtype conversion.  Replaces `call_ops_cast`
+ * (crates/hodu_cuda_kernels/src/kernels/ops_cast.rs:27-64) and
+ * `hodu_cuda_cast_{src}_to_{dst}` (crates/hodu_cuda_kernels/kernels/ops_cast.cu:7-30)
+ * for f32 <-> bf16 | f16 | f8e4m3 and i8 -> i32.
+ * metadata = [num_els, ndim, shape.., strides.., offset]
+ * (crates/hodu_core/src/op_metadatas.rs:1615-1640).
+ */
+int hodu_b200_cast(int device, void* stream, uint8_t src_dtype, uint8_t dst_dtype,
+                   const void* in, void* out,
+                   const size_t* metadata, size_t metadata_len);
+
+/*
+ * Fused gate/up half of a SwiGLU MLP:  out[M,N] = silu(x . w_gate) * (x . w_up).
+ * In the reference this is three launches and two [M,N] temporaries:
+ * `Linear::forward` twice (crates/hodu_nn/src/modules/linear.rs:38-47), `silu`
+ * (crates/hodu_cuda_kernels/kernels/ops_unary.cu:178, math.cuh:232-235) and `mul`
+ * (crates/hodu_cuda_kernels/kernels/ops_binary.cu).
+ * metadata = [M, K, N, x_stride_m, x_stride_k, wg_stride_k, wg_stride_n,
+ *             wu_stride_k, wu_stride_n, x_off, wg_off, wu_off]
+ * i.e. the dot wire format with a second right-hand operand.  dtype: bf16 | f16.
+ * `flags`: HODU_B200_SWIGLU_ROUND_EACH_OP or HODU_B200_SWIGLU_ROUND_ONCE.
+ */
+int hodu_b200_swiglu(int device, void* stream, uint8_t dtype,
+                     const void* x, const void* w_gate, const void* w_up, void* out,
+                     const size_t* metadata, size_t metadata_len, uint32_t flags);
+
+/*
+ * Host-buffer forms: the whole of "create tensors on the device, multiply, read
+ * the result back", i.e. `BackendDevice` upload (crates/hodu_core/src/be/device.rs:35-55),
+ * `call_ops_matmul` / `call_ops_dot`, then `to_cpu_storage`
+ * (crates/hodu_core/src/be_cuda/storage.rs:165-173), as one pipelined call.
+ * lhs/rhs/out are HOST pointers (pinned memory gives full copy speed); metadata
+ * describes the host operands exactly as in the device forms.  The call copies
+ * operands to device staging memory in slices, runs the same kernels as the
+ * device forms, copies results back, and returns after the output is complete.
+ * Only contiguous operands with offset 0 are accepted (what a freshly created
+ * tensor has).  Staging memory is allocated on first use and kept per device.
+ */
+int hodu_b200_matmul_host(int device, uint8_t in_dtype, uint8_t out_dtype,
+                          const void* lhs_host, const void* rhs_host, void* out_host,
+                          const size_t* metadata, size_t metadata_len,
+                          float scale_lhs, float scale_rhs);
+int hodu_b200_dot_host(int device, uint8_t in_dtype, uint8_t out_dtype,
+                       const void* lhs_host, const void* rhs_host, void* out_host,
+                       const size_t* metadata, size_t metadata_len,
+                       float scale_lhs, float scale_rhs);
+
+/* Text for an error code (static storage).  Mirrors `Display for CudaKernelError`
+ * (crates/hodu_cuda_kernels/src/error.rs:20-32). */
+const char* hodu_b200_strerror(int code);
+/* Longer message for the last failing call on the calling thread (thread-local). */
+const char* hodu_b200_last_error_message(void);
+
+/*
+ * Reads (and clears) the device status word of `device` after synchronising the
+ * device.  Zero means every kernel finished its waits; non-zero encodes which
+ * bounded wait gave up.  Returns HODU_B200_ERR_DEVICE_STATUS if the word was
+ * non-zero.  The reference has no counterpart: its kernels have no waits.
+ */
+int hodu_b200_last_status(int device, uint32_t* device_status_word);
+
+/* Testing aids (no reference counterpart). */
+int hodu_b200_force_path(int path);      /* process-wide; returns previous value  */
+int hodu_b200_last_path(void);           /* path taken by the last matmul/dot/swiglu
+                                            call on the calling thread            */
+uint64_t hodu_b200_launch_count(void);   /* kernels launched by this library so far */
+int hodu_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HODU_B200_H */
