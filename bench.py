@@ -1,0 +1,399 @@
+"""Benchmark of the matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+Default workload: configuration 2 of the benchmark list -- bf16 batched matmul
+A[16,2048,2048] @ B[16,2048,2048], f32 accumulate, bf16 output, seeded synthetic operands
+(N(0,1)/sqrt(2048), generated in f32 on the host, narrowed to bf16 on the device by this
+library's cast kernel).  One step = one call of `hodu_b200_matmul` on that input.
+With N > 1 ranks (torchrun, one per GPU) every rank runs the same per-GPU workload on its
+own operands (batches are independent: no collective on the compute path), so the
+whole-job value is the sum over ranks / the slowest rank's time ("weak" scaling).
+
+Prints ONE JSON line on rank 0.  `value` = device-resident throughput, `e2e` = the same
+metric through the host-buffer entry point (pinned host operands in, host result out, copies
+inside the timed region), `roofline` = achieved / measured tensor peak for the GEMM kernel,
+`cpu_baseline` = the reference's own CPU matmul (its C kernel over OpenBLAS sgemm, compiled
+from the reference sources into oracle/_ref) timed on this box's host cores.
+
+`--impl reference` times only that CPU implementation, on the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+WORKLOADS = {
+    "c1": "f32 matmul A[512,1024] @ B[1024,768] (config 1)",
+    "c2": "bf16 batched matmul A[16,2048,2048] @ B[16,2048,2048] -> bf16 (config 2)",
+    "c3": "f8e4m3 matmul A[8192,8192] @ B[8192,8192], scales 1/64 -> bf16 (config 3)",
+    "c4": "i8 matmul A[8192,8192] @ B[8192,8192] -> i32 (config 4)",
+    "c5": "SwiGLU MLP X[16384,4096], W_gate/W_up [4096,14336], W_down [14336,4096] bf16 (config 5)",
+}
+# DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
+# profiles/ (None until a capture of that workload exists).
+NCU_TRAFFIC_BYTES = {"c2": None, "c3": None, "c4": None, "c5": None, "c1": None}
+NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return {"burst": float(d["bf16_tflops"]), "sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "hbm_gbs": float(d.get("hbm_gbs", 0)), "source": "measured"}
+        except Exception:
+            pass
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with NVML while the timed region runs."""
+
+    def __init__(self, uuid: str):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------ reference CPU arm
+def cpu_reference_rate(workload: str, budget_s: float):
+    """Times the reference's CPU matmul (oracle/_ref: hodu_cpu_matmul_f32 / hodu_cpu_dot_f32 over
+    OpenBLAS sgemm; falls back to the oracle restatement's sgemm form if _ref is absent) on a
+    bounded sample of `workload`.  Returns (TFLOP/s, kind, cores, sample text, seconds)."""
+    from hodu_b200 import synthetic as S
+    from hodu_b200.layout import Layout
+    from hodu_b200.op_metadatas import dot_metadata, matmul_metadata
+    from oracle import oracle as O
+
+    ref = O.ref()
+    have_blas = ref is not None and ref.blas is not None
+    kind = "reference" if have_blas else "port"
+    cores = ref.blas_info()["threads"] if have_blas else (os.cpu_count() or 1)
+
+    def run(a, b, md, is_dot):
+        out = np.empty(int(md[0]) * int(md[2]) if is_dot else int(md[0]), dtype=np.float32)
+        t0 = time.perf_counter()
+        if have_blas:
+            ref.call("hodu_cpu_dot_f32" if is_dot else "hodu_cpu_matmul_f32", a, b, out, md)
+        else:
+            O.matmul(a, b, md, O.F32, is_dot=is_dot)
+        return time.perf_counter() - t0
+
+    rng = np.random.default_rng(0)
+    if workload == "c2":
+        d = 2048
+        one = Layout.from_shape((1, d, d))
+        a1 = (rng.standard_normal((1, d, d), dtype=np.float32) / 45.25).astype(np.float32)
+        b1 = (rng.standard_normal((1, d, d), dtype=np.float32) / 45.25).astype(np.float32)
+        t1 = run(a1, b1, matmul_metadata(one, one, one), False)            # warm-up + probe
+        t1 = min(t1, run(a1, b1, matmul_metadata(one, one, one), False))
+        nb = int(max(1, min(16, budget_s / max(t1, 1e-6))))
+        lay = Layout.from_shape((nb, d, d))
+        a = np.repeat(a1, nb, axis=0)
+        b = np.repeat(b1, nb, axis=0)
+        t = run(a, b, matmul_metadata(lay, lay, lay), False)
+        flops = 2.0 * nb * d ** 3
+        sample = f"{nb} of 16 batches of config 2 (operands widened to f32 beforehand, one hodu_cpu_matmul_f32 call)"
+    else:
+        shapes = {"c1": (512, 1024, 768), "c3": (8192, 8192, 8192), "c4": (8192, 8192, 8192), "c5": (16384, 4096, 14336)}
+        m, k, n = shapes[workload]
+        b = rng.standard_normal((k, n), dtype=np.float32)
+        probe_rows = min(m, 512)
+        a = rng.standard_normal((probe_rows, k), dtype=np.float32)
+        md = dot_metadata(Layout.from_shape(a.shape), Layout.from_shape(b.shape))
+        t1 = run(a, b, md, True)
+        t1 = min(t1, run(a, b, md, True))
+        rows = int(max(probe_rows, min(m, probe_rows * (budget_s / max(t1, 1e-6)))))
+        rows = max(128, rows // 128 * 128) if rows >= 128 else rows
+        a = rng.standard_normal((rows, k), dtype=np.float32)
+        md = dot_metadata(Layout.from_shape(a.shape), Layout.from_shape(b.shape))
+        t = run(a, b, md, True)
+        flops = 2.0 * rows * k * n * (3 if workload == "c5" and False else 1)
+        sample = f"{rows} of {m} rows of the {m}x{k}x{n} product (f32 operands, one hodu_cpu_dot_f32 call)"
+    return flops / t / 1e12, kind, cores, sample, t
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    per_step = max(0.05, min(3.0, 120.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_reference_rate(args.workload, per_step)
+    vals, secs = [], []
+    sample = kind = ""
+    cores = 1
+    for _ in range(args.steps):
+        v, kind, cores, sample, t = cpu_reference_rate(args.workload, per_step)
+        vals.append(v)
+        secs.append(t)
+    value = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": "matmul throughput", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOADS[args.workload], "note": "reference CPU path (hodu_cpu_kernels C kernel over OpenBLAS sgemm) on host cores; each step is a bounded sample"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------ GPU arm
+class Workload:
+    """Device-resident operands of one configuration plus the call that runs one step."""
+
+    def __init__(self, name: str, dev, stream_ptr: int):
+        import torch
+        from hodu_b200 import DType, Layout
+        from hodu_b200 import kernels as K
+        from hodu_b200 import synthetic as S
+        from hodu_b200.nn import Linear, SwiGluMlp
+        from hodu_b200.op_metadatas import cast_metadata, dot_metadata, matmul_metadata
+        from hodu_b200.tensor import Tensor
+
+        self.name, self.K, self.torch = name, K, torch
+        d0 = dev.index or 0
+
+        def cast_on_device(x32: np.ndarray, dt):
+            t = torch.from_numpy(x32).pin_memory().to(dev, non_blocking=True)
+            return Tensor.from_torch(t).to_dtype(dt).storage
+
+        if name == "c2":
+            c = S.config2()
+            self.a, self.b = cast_on_device(c["a"], DType.BF16), cast_on_device(c["b"], DType.BF16)
+            lay = Layout.from_shape(c["a"].shape)
+            self.md = matmul_metadata(lay, lay, lay)
+            self.out = torch.empty(lay.size(), dtype=torch.bfloat16, device=dev)
+            self.flops, self.dtype, self.launches = float(S.FLOPS[2]), "bf16", 1
+            self.in_dt, self.out_dt, self.scales, self.is_dot = DType.BF16, DType.BF16, (1.0, 1.0), False
+            self.step = lambda: K.call_ops_matmul(K.matmul.BF16, d0, self.a.data_ptr(), self.b.data_ptr(),
+                                                  self.out.data_ptr(), self.md, stream_ptr)
+        elif name in ("c3", "c4", "c1"):
+            c = {"c3": S.config3, "c4": S.config4, "c1": S.config1}[name]()
+            if name == "c3":
+                self.a, self.b = cast_on_device(c["a"], DType.F8E4M3), cast_on_device(c["b"], DType.F8E4M3)
+                self.in_dt, self.out_dt, self.scales, self.dtype = DType.F8E4M3, DType.BF16, (c["scale_a"], c["scale_b"]), "f8e4m3"
+            elif name == "c4":
+                self.a, self.b = torch.from_numpy(c["a"]).to(dev).reshape(-1), torch.from_numpy(c["b"]).to(dev).reshape(-1)
+                self.in_dt, self.out_dt, self.scales, self.dtype = DType.I8, DType.I32, (1.0, 1.0), "i8"
+            else:
+                self.a, self.b = torch.from_numpy(c["a"]).to(dev).reshape(-1), torch.from_numpy(c["b"]).to(dev).reshape(-1)
+                self.in_dt, self.out_dt, self.scales, self.dtype = DType.F32, DType.F32, (1.0, 1.0), "f32"
+            m, k = c["a"].shape
+            n = c["b"].shape[1]
+            self.md = dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n)))
+            from hodu_b200.dtype import to_torch
+            self.out = torch.empty(m * n, dtype=to_torch(self.out_dt), device=dev)
+            self.flops, self.launches, self.is_dot = 2.0 * m * n * k, 1, True
+            self.step = lambda: K.call_ops_matmul_ex(self.in_dt, self.out_dt, d0, self.a.data_ptr(), self.b.data_ptr(),
+                                                     self.out.data_ptr(), self.md, self.scales[0], self.scales[1],
+                                                     stream_ptr, is_dot=True)
+        elif name == "c5":
+            c = S.config5()
+            x = Tensor(cast_on_device(c["x"], DType.BF16), Layout.from_shape(c["x"].shape))
+            lin = lambda w: Linear(Tensor(cast_on_device(np.ascontiguousarray(w.T), DType.BF16), Layout.from_shape(w.T.shape)))
+            self.mlp = SwiGluMlp(lin(c["w_gate"]), lin(c["w_up"]), lin(c["w_down"]))
+            self.x = x
+            self.flops, self.dtype, self.launches = float(S.FLOPS[5]), "bf16", 2
+            self.step = lambda: self.mlp.forward(self.x)
+            self.md = None
+        else:
+            raise SystemExit(f"unknown workload {name}")
+
+    def host_buffers(self):
+        """Pinned host copies of the operands and a pinned result buffer (for the e2e leg)."""
+        torch = self.torch
+        ha = self.a.view(torch.uint8).cpu().pin_memory()
+        hb = self.b.view(torch.uint8).cpu().pin_memory()
+        ho = torch.empty(self.out.numel() * self.out.element_size(), dtype=torch.uint8).pin_memory()
+        return ha, hb, ho
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from hodu_b200 import _lib
+    from hodu_b200 import kernels as K
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    _lib.lib()  # fails loudly if libhodu_b200.so is missing
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    warmup = max(3, args.warmup)
+    stream = torch.cuda.current_stream(dev)
+    wl = Workload(args.workload, dev, stream.cuda_stream)
+    for _ in range(warmup):
+        wl.step()
+    torch.cuda.synchronize(dev)
+    K.last_status(local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize(dev)
+
+    uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    launches0 = K.launch_count()
+    with ClockSampler(uuid) as clocks:
+        e0.record(stream)
+        for _ in range(args.steps):
+            wl.step()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+    barrier()
+    launches = K.launch_count() - launches0
+    K.last_status(local)
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    ms_per_step = ms_max / args.steps
+    value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
+
+    # ---- e2e through the host-buffer entry point ------------------------------------------------
+    e2e = None
+    if args.workload in ("c2", "c3", "c4", "c1"):
+        ha, hb, ho = wl.host_buffers()
+        call = lambda: K.call_ops_matmul_host(wl.in_dt, wl.out_dt, local, ha.data_ptr(), hb.data_ptr(), ho.data_ptr(),
+                                              wl.md, wl.scales[0], wl.scales[1], is_dot=wl.is_dot)
+        for _ in range(3):
+            call()
+        barrier()
+        n_e2e = max(1, min(args.steps, args.e2e_steps))
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            call()  # returns when the result is complete in host memory
+        torch.cuda.synchronize(dev)
+        dt_ms = (time.perf_counter() - t0) * 1e3
+        tt = torch.tensor([dt_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item()) / n_e2e
+        e2e = {"value": wl.flops * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(ha.numel() + hb.numel()), "d2h_bytes_per_step": int(ho.numel()),
+               "ms_per_step": e2e_ms, "steps": n_e2e,
+               "api": "hodu_b200_matmul_host / hodu_b200_dot_host (pinned host operands, host result; wall clock around the blocking call)"}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    peaks = measured_peaks()
+    timed_s = ms_total * 1e-3
+    if args.workload in ("c2", "c5"):
+        peak_kind = "burst" if timed_s < 1.0 else "sustained"
+        peak, peak_src = peaks[peak_kind], f"{peaks['source']} cuBLAS bf16 {peak_kind} (MEASURED_PEAKS.json)" if peaks["source"] == "measured" else "fallback 1590 burst / 1400 sustained"
+    else:
+        peak, peak_src = NOMINAL_PEAK_TFLOPS[args.workload], "nominal dense peak for this dtype (no measured figure for it)"
+    achieved = wl.flops / (ms_total / args.steps * 1e-3) / 1e12  # this rank, per launch group
+    line = {
+        "metric": "matmul throughput", "value": value, "unit": "TFLOP/s" if args.workload != "c4" else "TOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": WORKLOADS[args.workload], "per_gpu": "the whole configuration on every GPU (independent batches / rows, no collective)",
+                   "l2": "operands + output exceed the 126 MB L2 (no flush needed)" if args.workload != "c1" else "fits in L2 (latency-bound case)",
+                   "timing": "CUDA events on the launching stream around all timed steps, max over ranks"},
+        "clocks": clocks.summary(),
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES[args.workload], "peak_source": peak_src,
+                     "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS[args.workload]},
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world == 1 and not args.no_cpu_baseline:
+        v, kind, cores, sample, secs = cpu_reference_rate(args.workload, 15.0)
+        line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample, "seconds": secs}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -28,6 +28,7 @@ SIGNATURES = {
     "hodu_b200_strerror": (C.c_char_p, [_i]),
     "hodu_b200_last_error_message": (C.c_char_p, []),
     "hodu_b200_last_status": (_i, [_i, C.POINTER(C.c_uint32)]),
+    "hodu_b200_debug_wait_timeout": (_i, [_i, _vp, _u32]),
     "hodu_b200_force_path": (_i, [_i]),
     "hodu_b200_last_path": (_i, []),
     "hodu_b200_launch_count": (C.c_uint64, []),

@@ -281,11 +281,7 @@ int hodu_b200_dot_ex(int device, void* stream, uint8_t in_dtype, uint8_t out_dty
 
 int hodu_b200_cast(int device, void* stream, uint8_t src, uint8_t dst, const void* in, void* out,
                    const size_t* md, size_t len) {
-  DeviceState* st = device_state(device);
-  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
-  DeviceGuard guard(device);
-  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
-  return launch_cast(src, dst, in, out, md, len, st, static_cast<cudaStream_t>(stream));
+  return launch_cast(src, dst, in, out, md, len, device, static_cast<cudaStream_t>(stream));
 }
 
 int hodu_b200_swiglu(int device, void* stream, uint8_t dtype, const void* x, const void* w_gate,
@@ -342,6 +338,15 @@ int hodu_b200_last_status(int device, uint32_t* word) {
   if (word) *word = w;
   if (w != 0) return fail(HODU_B200_ERR_DEVICE_STATUS, "device status word 0x%08x (cta %u, wait %u)", w, (w >> 4) & 0xFFFFu, w & 0xFu);
   return 0;
+}
+
+int hodu_b200_debug_wait_timeout(int device, void* stream, uint32_t limit_ms) {
+  if (limit_ms == 0 || limit_ms > 2000) return fail(HODU_B200_ERR_INVALID_INPUT, "limit_ms must be 1..2000");
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+  return launch_wait_timeout_probe(st, static_cast<cudaStream_t>(stream), limit_ms);
 }
 
 int hodu_b200_force_path(int path) {

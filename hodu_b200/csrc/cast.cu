@@ -113,7 +113,7 @@ int run_cast(const void* in_base, void* out, size_t n, bool contiguous, const St
 }  // namespace
 
 int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, size_t md_len,
-                DeviceState* st, cudaStream_t stream) {
+                int device, cudaStream_t stream) {
   if (!md || md_len < 3) return fail(HODU_B200_ERR_INVALID_INPUT, "cast: metadata too short");
   const size_t n = md[0], ndim = md[1];
   if (md_len != 3 + 2 * ndim)
@@ -151,6 +151,15 @@ int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, s
     m.ndim = k;
   }
   const uint8_t* base = static_cast<const uint8_t*>(in) + offset * dtype_size(src);
+  const bool known = (src == HODU_DTYPE_F32 && (dst == HODU_DTYPE_BF16 || dst == HODU_DTYPE_F16 || dst == HODU_DTYPE_F8E4M3)) ||
+                     (dst == HODU_DTYPE_F32 && (src == HODU_DTYPE_BF16 || src == HODU_DTYPE_F16 || src == HODU_DTYPE_F8E4M3)) ||
+                     (src == HODU_DTYPE_I8 && dst == HODU_DTYPE_I32);
+  if (!known) return fail(HODU_B200_ERR_INVALID_KERNEL, "cast: unsupported pair %s -> %s", dtype_name(src), dtype_name(dst));
+  // Arguments are valid: only now is the device touched.
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
 
 #define HODU_CAST(SD, DD, S, D) \
   if (src == SD && dst == DD) return run_cast<S, D>(base, out, n, contiguous, m, st, stream)

@@ -88,6 +88,8 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream);
 // tcgen05 kernel. Returns 1 if the layout cannot be described to TMA (nothing
 // launched, `why` says which rule failed), 0 when launched, <0 on error.
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// One tiny kernel whose only wait can never be satisfied; it gives up after limit_ms.
+int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t limit_ms);
 // Parsers of the reference's wire formats and the path chooser (api.cu).
 int parse_matmul(const size_t* md, size_t len, Problem* pb);
 int parse_dot(const size_t* md, size_t len, Problem* pb);
@@ -98,6 +100,6 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream);
 void release_host_pipeline(int device);
 // Casts.
 int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, size_t md_len,
-                DeviceState* st, cudaStream_t stream);
+                int device, cudaStream_t stream);
 
 }  // namespace hodu_b200

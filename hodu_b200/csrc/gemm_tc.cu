@@ -80,7 +80,7 @@ struct TcParams {
 // -------------------------------------------------------------- bounded waits
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
                                              volatile uint32_t* abort_flag, uint32_t* status,
-                                             uint32_t code) {
+                                             uint32_t code, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t i = 1;; ++i) {
@@ -90,7 +90,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0u, code);
         return false;
@@ -418,6 +418,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// A wait that nothing satisfies: shows, without faulting or hanging anything, that a
+// bounded wait gives up, records its code and lets the kernel return normally.
+__global__ void wait_timeout_probe_kernel(uint32_t* status, uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    wait_bounded(smem_u32(&bar), 0u, &abort_flag, status, 0x80000000u | 7u, limit_ns);
+  __syncthreads();
+}
+
 // -------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -601,6 +617,13 @@ int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
 }
 
 }  // namespace
+
+int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t limit_ms) {
+  wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(st->status, static_cast<uint64_t>(limit_ms) * 1000000ull);
+  HODU_CUDA_TRY(cudaGetLastError(), HODU_B200_ERR_LAUNCH);
+  count_launch();
+  return 0;
+}
 
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
   static const char* none = "";

@@ -30,10 +30,15 @@ def all_gather_rows(local: torch.Tensor, total_rows: int, group=None) -> torch.T
     import torch.distributed as dist
     world = dist.get_world_size(group)
     sizes = [shard_range(total_rows, r, world) for r in range(world)]
-    full = local.new_empty((total_rows, *local.shape[1:]))
-    parts = [full.narrow(0, lo, hi - lo) for lo, hi in sizes]
-    if len({hi - lo for lo, hi in sizes}) == 1:
+    rows = [hi - lo for lo, hi in sizes]
+    if len(set(rows)) == 1:
+        full = local.new_empty((total_rows, *local.shape[1:]))
         dist.all_gather_into_tensor(full, local.contiguous(), group=group)
-    else:
-        dist.all_gather(parts, local.contiguous(), group=group)
-    return full
+        return full
+    # ragged shards: pad every shard to the largest, gather, drop the padding
+    most = max(rows)
+    padded = local.new_zeros((most, *local.shape[1:]))
+    padded[: local.shape[0]] = local
+    gathered = local.new_empty((world * most, *local.shape[1:]))
+    dist.all_gather_into_tensor(gathered, padded, group=group)
+    return torch.cat([gathered[r * most: r * most + rows[r]] for r in range(world)], dim=0)

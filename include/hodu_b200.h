@@ -210,6 +210,11 @@ int hodu_b200_last_status(int device, uint32_t* device_status_word);
 int hodu_b200_force_path(int path);      /* process-wide; returns previous value  */
 int hodu_b200_last_path(void);           /* path taken by the last matmul/dot/swiglu
                                             call on the calling thread            */
+/* Launches one tiny kernel whose only wait can never be satisfied and whose limit is
+ * `limit_ms` (1..2000): the wait gives up, the kernel records a code in the status word
+ * and returns normally.  hodu_b200_last_status then reports it.  Exercises the
+ * bounded-wait mechanism of the GEMM kernels without faulting or hanging anything. */
+int hodu_b200_debug_wait_timeout(int device, void* stream, uint32_t limit_ms);
 uint64_t hodu_b200_launch_count(void);   /* kernels launched by this library so far */
 int hodu_b200_version(void);
 

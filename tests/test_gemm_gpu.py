@@ -1,0 +1,204 @@
+"""Parity of the CUDA matmul / dot path with the CPU oracle, through the C ABI.
+
+Bars: integer outputs bit-exact; bf16 / f16 max|got-want| / max|want| <= 1e-2; f8e4m3 inputs
+<= 6e-2 of output scale; f32 <= 1e-4.  The oracle widens to f32, multiplies with sgemm and
+narrows once with round-to-nearest-even."""
+import numpy as np
+import pytest
+
+from gpu_util import check_close, gpu_matmul
+from hodu_b200 import CudaKernelError, Layout, _lib
+from hodu_b200.op_metadatas import dot_metadata, matmul_metadata
+from oracle import oracle as O
+from test_oracle import KNOWN
+
+pytestmark = pytest.mark.gpu
+
+TOL = {O.BF16: 1e-2, O.F16: 1e-2, O.F8E4M3: 6e-2, O.F32: 1e-4}
+AUTO, SIMT, TENSOR = _lib.PATH_AUTO, _lib.PATH_SIMT, _lib.PATH_TENSOR
+
+
+def rand_storage(rng, dtype, shape):
+    if dtype in (O.I8,):
+        return rng.integers(-127, 128, size=shape, dtype=np.int8)
+    if dtype == O.I32:
+        return rng.integers(-1000, 1000, size=shape).astype(np.int32)
+    x = rng.standard_normal(shape).astype(np.float32)
+    if dtype == O.F8E4M3:
+        x = np.clip(x * 16, -448, 448)
+    return O.narrow(x, dtype)
+
+
+def operand(rng, dtype, rows, cols, contiguous_index):
+    """A [rows, cols] operand whose `contiguous_index` ('r' or 'c') has stride 1."""
+    if contiguous_index == "c":
+        return rand_storage(rng, dtype, (rows, cols)), Layout.from_shape((rows, cols))
+    return rand_storage(rng, dtype, (cols, rows)), Layout.from_shape((cols, rows)).transpose(0, 1)
+
+
+@pytest.mark.parametrize("case", KNOWN, ids=[c[0] for c in KNOWN])
+def test_reference_known_answers(case):
+    """The reference's eight f32 known-answer tests, same metadata vectors, plain API."""
+    _, is_dot, lhs, rhs, md, want = case
+    got, _ = gpu_matmul(np.array(lhs, np.float32), np.array(rhs, np.float32), md, O.F32, is_dot=is_dot, plain_api=True)
+    assert np.array_equal(np.round(got * 1e4) / 1e4, np.array(want, np.float32))
+
+
+PAIRS = [(O.BF16, O.BF16), (O.F16, O.F16), (O.F8E4M3, O.BF16), (O.F8E4M3, O.F8E4M3), (O.F8E4M3, O.F32),
+         (O.I8, O.I32), (O.I8, O.I8), (O.BF16, O.F32), (O.F16, O.F32), (O.F8E4M3, O.F16)]
+SHAPES = [(128, 128, 256), (200, 136, 328), (1, 256, 128), (129, 2064, 72), (512, 512, 512), (130, 8, 16)]
+
+
+@pytest.mark.parametrize("in_dt,out_dt", PAIRS)
+@pytest.mark.parametrize("a_c,b_c", [("c", "c"), ("c", "r"), ("r", "c"), ("r", "r")])
+def test_tensor_core_path_all_layouts(in_dt, out_dt, a_c, b_c):
+    rng = np.random.default_rng(1000 * in_dt + 10 * out_dt + (a_c == "r") * 2 + (b_c == "r"))
+    for (m, k, n) in SHAPES:
+        # TMA needs 16-byte pitches: round the extent that becomes a pitch
+        unit = 16 // O.NP_STORAGE[in_dt]().itemsize
+        if (a_c == "c" and m > 1) or b_c == "r":
+            k = (k + unit - 1) // unit * unit
+        if a_c == "r":
+            m = (m + unit - 1) // unit * unit if k > 1 else m
+        if b_c == "c":
+            n = (n + unit - 1) // unit * unit
+        a, la = operand(rng, in_dt, m, k, a_c)
+        b, lb = operand(rng, in_dt, k, n, b_c)
+        md = dot_metadata(la, lb)
+        scales = (0.5, 0.25) if in_dt == O.F8E4M3 else (1.0, 1.0)
+        got, path = gpu_matmul(a, b, md, in_dt, out_dt, scales, is_dot=True, path=TENSOR)
+        assert path == TENSOR
+        want = O.matmul(a, b, md, in_dt, out_dt, scales[0] * scales[1], is_dot=True)
+        tol = TOL.get(in_dt, 0) if out_dt != O.F8E4M3 else 7e-2  # e4m3 output: half an ulp at the top is 1/16
+        check_close(got, want, out_dt, tol)
+
+
+@pytest.mark.parametrize("in_dt,out_dt", PAIRS + [(O.F32, O.F32), (O.I32, O.I32)])
+def test_simt_path_any_strides(in_dt, out_dt):
+    """Pitches and offsets TMA cannot describe: odd extents, element offsets, padded rows."""
+    rng = np.random.default_rng(77 + in_dt + out_dt)
+    for (m, k, n, pad, off) in [(2, 3, 2, 0, 0), (37, 53, 29, 0, 0), (65, 70, 130, 3, 5), (1, 1, 1, 0, 1), (64, 16, 64, 1, 0)]:
+        a = rand_storage(rng, in_dt, (off + m * (k + pad),))
+        b = rand_storage(rng, in_dt, (off + k * (n + pad),))
+        la = Layout((m, k), (k + pad, 1), off)
+        lb = Layout((k, n), (n + pad, 1), off)
+        md = dot_metadata(la, lb)
+        got, path = gpu_matmul(a, b, md, in_dt, out_dt, is_dot=True, path=SIMT)
+        assert path == SIMT
+        want = O.matmul(a, b, md, in_dt, out_dt, is_dot=True)
+        check_close(got, want, out_dt, TOL.get(in_dt, 0) if out_dt != O.F8E4M3 else 7e-2)
+        # element-by-element C restatement on the small ones
+        if m * n * k < 200000:
+            want_c = O.matmul_c(a, b, md, in_dt, out_dt, is_dot=True)
+            check_close(got, want_c, out_dt, TOL.get(in_dt, 0) if out_dt != O.F8E4M3 else 7e-2)
+
+
+@pytest.mark.parametrize("in_dt,out_dt", [(O.BF16, O.BF16), (O.F8E4M3, O.BF16), (O.I8, O.I32)])
+def test_both_gpu_paths_agree(in_dt, out_dt):
+    rng = np.random.default_rng(5)
+    a, la = operand(rng, in_dt, 256, 384, "c")
+    b, lb = operand(rng, in_dt, 384, 256, "c")
+    md = dot_metadata(la, lb)
+    t, _ = gpu_matmul(a, b, md, in_dt, out_dt, is_dot=True, path=TENSOR)
+    s, _ = gpu_matmul(a, b, md, in_dt, out_dt, is_dot=True, path=SIMT)
+    check_close(t, s, out_dt, 4e-3)  # both accumulate in f32; they differ by summation order and one bf16 ulp
+
+
+BATCH_CASES = [
+    # (lhs shape, rhs shape) -- broadcasting over batch dims, right-aligned
+    ((3, 128, 64), (3, 64, 128)),
+    ((3, 128, 64), (64, 128)),            # rhs 2-D, as in the reference's CUDA batch test
+    ((1, 136, 64), (4, 64, 72)),          # lhs broadcast
+    ((2, 3, 128, 64), (2, 3, 64, 128)),
+    ((2, 1, 128, 64), (1, 3, 64, 128)),   # both broadcast, different dims
+    ((2, 3, 4, 40, 64), (4, 64, 48)),
+]
+
+
+@pytest.mark.parametrize("lshape,rshape", BATCH_CASES)
+@pytest.mark.parametrize("in_dt,out_dt", [(O.BF16, O.BF16), (O.I8, O.I32), (O.F32, O.F32)])
+@pytest.mark.parametrize("as_views", [False, True])
+def test_batched_broadcast(lshape, rshape, in_dt, out_dt, as_views):
+    """as_views: both operands broadcast to the full batch shape with stride-0 dims, which is
+    what Tensor::matmul passes (tensor/ops/matrix.rs:155-167)."""
+    rng = np.random.default_rng(len(lshape) * 100 + len(rshape) + in_dt)
+    a, b = rand_storage(rng, in_dt, lshape), rand_storage(rng, in_dt, rshape)
+    la, lb = Layout.from_shape(lshape), Layout.from_shape(rshape)
+    nb = max(len(lshape), len(rshape)) - 2
+    lb_dims = (1,) * (nb - (len(lshape) - 2)) + tuple(lshape[:-2])
+    rb_dims = (1,) * (nb - (len(rshape) - 2)) + tuple(rshape[:-2])
+    batch = tuple(max(x, y) for x, y in zip(lb_dims, rb_dims))
+    if as_views:
+        la = la.broadcast_to((*batch, *lshape[-2:]))
+        lb = lb.broadcast_to((*batch, *rshape[-2:]))
+    out_l = Layout.from_shape((*batch, lshape[-2], rshape[-1]))
+    md = matmul_metadata(la, lb, out_l)
+    want = O.matmul(a, b, md, in_dt, out_dt)
+    esize = np.dtype(O.NP_STORAGE[in_dt]).itemsize
+    tma_ok = all((d * esize) % 16 == 0 for d in (lshape[-1], rshape[-1]))  # row pitches TMA can take
+    paths = [SIMT] if (in_dt == O.F32 or not tma_ok) else [SIMT, TENSOR]
+    for path in paths:
+        got, taken = gpu_matmul(a, b, md, in_dt, out_dt, path=path)
+        assert taken == path
+        check_close(got, want, out_dt, TOL.get(in_dt, 0))
+    if int(np.prod(out_l.shape)) * lshape[-1] < 300000:
+        check_close(want, O.matmul_c(a, b, md, in_dt, out_dt), out_dt, TOL.get(in_dt, 0))
+
+
+def test_offsets_on_tensor_path():
+    """Views into a larger buffer: 16-byte-aligned element offsets and padded pitches."""
+    rng = np.random.default_rng(3)
+    m, k, n, pitch_a, pitch_b = 160, 192, 136, 200, 144
+    a = rand_storage(rng, O.BF16, (64 + m * pitch_a,))
+    b = rand_storage(rng, O.BF16, (24 + k * pitch_b,))
+    md = dot_metadata(Layout((m, k), (pitch_a, 1), 64), Layout((k, n), (pitch_b, 1), 24))
+    got, path = gpu_matmul(a, b, md, O.BF16, is_dot=True, path=TENSOR)
+    check_close(got, O.matmul(a, b, md, O.BF16, is_dot=True), O.BF16, 1e-2)
+
+
+def test_auto_path_selection_and_refusal():
+    rng = np.random.default_rng(4)
+    # large aligned -> tensor cores
+    a, la = operand(rng, O.BF16, 256, 256, "c")
+    b, lb = operand(rng, O.BF16, 256, 256, "c")
+    _, path = gpu_matmul(a, b, dot_metadata(la, lb), O.BF16, is_dot=True)
+    assert path == TENSOR
+    # K = 37: row pitch of 74 bytes cannot be a TMA stride -> CUDA-core kernel, same answer bar
+    a, la = operand(rng, O.BF16, 256, 37 * 8 + 1, "c")
+    b, lb = operand(rng, O.BF16, 37 * 8 + 1, 256, "c")
+    md = dot_metadata(la, lb)
+    got, path = gpu_matmul(a, b, md, O.BF16, is_dot=True)
+    assert path == SIMT
+    check_close(got, O.matmul(a, b, md, O.BF16, is_dot=True), O.BF16, 1e-2)
+    with pytest.raises(CudaKernelError) as e:
+        gpu_matmul(a, b, md, O.BF16, is_dot=True, path=TENSOR)
+    assert e.value.kind == "invalid input" and "tensor-core path refused" in str(e.value)
+    # f32 has no tensor-core kernel
+    a, la = operand(rng, O.F32, 256, 256, "c")
+    _, path = gpu_matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)
+    assert path == SIMT
+
+
+def test_aliased_inputs_and_k_zero():
+    rng = np.random.default_rng(6)
+    a, la = operand(rng, O.BF16, 128, 128, "c")
+    md = dot_metadata(la, la)
+    got, _ = gpu_matmul(a, a, md, O.BF16, is_dot=True, path=TENSOR)  # a.matmul(&a)
+    check_close(got, O.matmul(a, a, md, O.BF16, is_dot=True), O.BF16, 1e-2)
+    # K == 0: an empty sum is zero
+    md0 = dot_metadata(Layout.from_shape((4, 0)), Layout.from_shape((0, 5)))
+    got, _ = gpu_matmul(np.zeros(1, np.float32), np.zeros(1, np.float32), md0, O.F32, is_dot=True)
+    assert np.array_equal(got, np.zeros(20, np.float32))
+
+
+def test_saturation_of_e4m3_output():
+    """Sums beyond +-448 saturate to the largest finite e4m3, they do not become NaN."""
+    k = 128
+    a = O.narrow(np.full((128, k), 16.0, np.float32), O.F8E4M3)
+    b = O.narrow(np.full((k, 128), 16.0, np.float32), O.F8E4M3)
+    b[:, 64:] ^= 0x80  # negative half
+    md = dot_metadata(Layout.from_shape((128, k)), Layout.from_shape((k, 128)))
+    for path in (TENSOR, SIMT):
+        got, _ = gpu_matmul(a, b, md, O.F8E4M3, O.F8E4M3, is_dot=True, path=path)
+        g = got.reshape(128, 128)
+        assert np.all(g[:, :64] == 0x7E) and np.all(g[:, 64:] == 0xFE)
