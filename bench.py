@@ -336,7 +336,7 @@ def main():
 
     # ---- e2e through the host-buffer entry point ------------------------------------------------
     e2e = None
-    if args.workload in ("c2", "c3", "c4", "c1"):
+    if args.workload in ("c2", "c3", "c4", "c1") and args.e2e_steps > 0:
         ha, hb, ho = wl.host_buffers()
         call = lambda: K.call_ops_matmul_host(wl.in_dt, wl.out_dt, local, ha.data_ptr(), hb.data_ptr(), ho.data_ptr(),
                                               wl.md, wl.scales[0], wl.scales[1], is_dot=wl.is_dot)

@@ -3,6 +3,7 @@
 // for the contract of each entry point and the reference interface it replaces.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -42,7 +43,16 @@ const char* dtype_name(int dt) {
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 void set_last_path(int path) { g_last_path = path; }
-int forced_path() { return g_forced_path.load(std::memory_order_relaxed); }
+int forced_path() {
+  // HODU_B200_FORCE_PATH=<n> presets the selector (same values as hodu_b200_force_path).
+  static const bool env_read = [] {
+    const char* e = getenv("HODU_B200_FORCE_PATH");
+    if (e && e[0] >= '0' && e[0] <= '4' && e[1] == 0) g_forced_path.store(e[0] - '0');
+    return true;
+  }();
+  (void)env_read;
+  return g_forced_path.load(std::memory_order_relaxed);
+}
 
 DeviceGuard::DeviceGuard(int device) {
   if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; }
@@ -189,15 +199,15 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   if (pb.K == 0) { set_last_path(HODU_B200_PATH_AUTO); return zero_output(pb, stream); }
   const int forced = forced_path();
   const long long work = static_cast<long long>(pb.M) * pb.N * pb.K * pb.batches;
-  const bool want_tc = forced == HODU_B200_PATH_TENSOR ||
-                       (forced == HODU_B200_PATH_AUTO && work >= kTensorMinWork);
+  const bool forced_tc = forced == HODU_B200_PATH_TENSOR || forced == HODU_B200_PATH_TENSOR_1CTA ||
+                         forced == HODU_B200_PATH_TENSOR_2CTA;
+  const bool want_tc = forced_tc || (forced == HODU_B200_PATH_AUTO && work >= kTensorMinWork);
   if (want_tc) {
     const char* why = "";
     const int r = launch_gemm_tc(pb, st, stream, &why);
     if (r == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
     if (r < 0) return r;
-    if (forced == HODU_B200_PATH_TENSOR)
-      return fail(HODU_B200_ERR_INVALID_INPUT, "tensor-core path refused: %s", why);
+    if (forced_tc) return fail(HODU_B200_ERR_INVALID_INPUT, "tensor-core path refused: %s", why);
   }
   set_last_path(HODU_B200_PATH_SIMT);
   return launch_gemm_simt(pb, st, stream);
@@ -350,7 +360,7 @@ int hodu_b200_debug_wait_timeout(int device, void* stream, uint32_t limit_ms) {
 }
 
 int hodu_b200_force_path(int path) {
-  if (path < HODU_B200_PATH_AUTO || path > HODU_B200_PATH_TENSOR) return HODU_B200_ERR_INVALID_INPUT;
+  if (path < HODU_B200_PATH_AUTO || path > HODU_B200_PATH_TENSOR_2CTA) return HODU_B200_ERR_INVALID_INPUT;
   return g_forced_path.exchange(path);
 }
 int hodu_b200_last_path(void) { return g_last_path; }

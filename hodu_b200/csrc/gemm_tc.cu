@@ -22,6 +22,9 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <stdio.h>
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -32,16 +35,17 @@ using namespace ptx;
 
 namespace {
 
-constexpr int BM = 128;                 // tile rows == TMEM lanes
-constexpr int kThreads = 192;
-constexpr int kStageA = BM * 128;       // bytes: 128 rows (or MN elements) x 128 B of K
+constexpr int BM = 128;                 // rows of A one CTA stages == TMEM lanes
+constexpr int kThreads = 224;           // 7 warps, see the role table above
+constexpr int kStageA = BM * 128;       // bytes: 128 rows (or M elements) x 128 B of K
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, OUT_I8 = 5 };
 
-template <int BN> struct TileCfg {
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kStageB = BN * 128;
+// Stage ring per CTA.  PAIR: each CTA of the pair stages 128 columns of B.
+template <int BN, bool PAIR> struct TileCfg {
+  static constexpr int kStageB = PAIR ? 128 * 128 : BN * 128;
+  static constexpr int kStages = PAIR ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
 };
 
@@ -55,27 +59,51 @@ struct SmemTail {
   uint32_t abort_flag;
 };
 
+// How one operand is staged and described to the tensor core.
+struct OperandLoad {
+  uint32_t mn_major;   // 0: K contiguous, 1: M/N contiguous
+  uint32_t slab_dim;   // MN-major only: the 128-byte slabs are a tensor-map dimension (one box per stage)
+  uint32_t boxes;      // TMA boxes per stage (per CTA)
+  uint32_t box_bytes;
+  uint32_t box_mn;     // M/N elements covered by one box
+  uint32_t inner;      // elements per 128 bytes
+  uint32_t bmul[3];    // 0 where the operand broadcasts that (collapsed) batch dim
+  uint32_t desc_hi;    // smem matrix descriptor bits 32..63
+  uint32_t desc_lo;    // bits 14..31 (leading byte offset field)
+  uint32_t kstep16;    // start-address advance per MMA, in 16-byte units
+};
+
 struct TcParams {
   uint32_t M, N, K;
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks, group_m;
-  uint32_t bdim1, bdim2;                 // batch = (b0 * bdim1 + b1) * bdim2 + b2
-  uint32_t a_bmul[3], b_bmul[3];         // 0 where the operand broadcasts that batch dim
-  uint32_t a_mn_major, b_mn_major;
-  uint32_t a_boxes, b_boxes;             // TMA boxes per stage
-  uint32_t a_box_bytes, b_box_bytes;
-  uint32_t a_box_mn, b_box_mn;           // M / N elements covered by one box
-  uint32_t bk;                           // K elements per stage (128 bytes worth)
-  uint32_t a_desc_hi, b_desc_hi;         // smem descriptor bits 32..63
-  uint32_t a_desc_lo, b_desc_lo;         // smem descriptor bits 14..31 (leading byte offset)
-  uint32_t a_kstep16, b_kstep16;         // start-address advance per MMA, 16-byte units
+  uint32_t bdim1, bdim2;  // batch = (b0 * bdim1 + b1) * bdim2 + b2
+  uint32_t bk;            // K elements per stage (128 bytes worth)
+  OperandLoad a, b;
   uint32_t idesc;
-  uint32_t out_vec_ok;                   // rows of `out` allow 16-byte stores
+  uint32_t out_vec_ok;    // rows of `out` allow 16-byte stores
   uint32_t swiglu_flags;
   float alpha;
   unsigned long long ldc, out_batch_stride;  // elements
   void* out;
   uint32_t* status;
 };
+
+// Optional per-role wait accounting (compile with -DHODU_TC_PROFILE): cycles the roles of
+// CTA 0 and 1 spend inside their waits, read back with hodu_b200_debug_read_prof.
+#ifdef HODU_TC_PROFILE
+__device__ unsigned long long g_tc_prof[64];
+#define PROF_DECL long long prof_wait = 0, prof_t0 = clock64(), prof_tmp
+#define PROF_WAIT(expr) (prof_tmp = clock64(), ok = (expr), prof_wait += clock64() - prof_tmp, ok)
+#define PROF_DUMP(slot)                                                 \
+  if (blockIdx.x < 2) {                                                 \
+    g_tc_prof[(blockIdx.x * 4 + (slot)) * 2] = prof_wait;               \
+    g_tc_prof[(blockIdx.x * 4 + (slot)) * 2 + 1] = clock64() - prof_t0; \
+  }
+#else
+#define PROF_DECL
+#define PROF_WAIT(expr) (ok = (expr))
+#define PROF_DUMP(slot)
+#endif
 
 // -------------------------------------------------------------- bounded waits
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
@@ -207,16 +235,95 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* dst, const uint32_t (&v
   }
 }
 
+// -------------------------------------------------------------- producer
+// One thread streams ONE operand (A or B) of every tile of this CTA into the stage ring.
+// The two operands have a producer warp each, so the per-stage issue cost (barrier wait,
+// expect-tx arrive, TMA issue) of one never delays the other.
+//   PAIR: both CTAs of the pair signal CTA 0's `full` barriers; only CTA 0's producers
+//   arrive on them (with the byte count of both CTAs), CTA 1's just issue their loads.
+template <int BN, bool SWIGLU, bool PAIR, bool IS_A>
+__device__ __forceinline__ void producer_role(const TcParams& p, const OperandLoad& o,
+                                              const CUtensorMap* map0, const CUtensorMap* map1,
+                                              SmemTail* tail, uint32_t smem_operand, uint32_t rank,
+                                              uint32_t first_tile, uint32_t tile_step,
+                                              uint32_t code) {
+  using Cfg = TileCfg<BN, PAIR>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr uint32_t kStageBytes = IS_A ? kStageA : Cfg::kStageB;
+  constexpr uint32_t kOutCols = SWIGLU ? BN / 2 : BN;
+  volatile uint32_t* abort_flag = &tail->abort_flag;
+  const uint32_t my_bytes = o.boxes * o.box_bytes;
+  const uint32_t full0 = PAIR ? mapa_shared(smem_u32(&tail->full[0]), 0u) : smem_u32(&tail->full[0]);
+  uint32_t s = 0, ph = 0, issued = 0;
+  bool ok = true;
+  PROF_DECL;
+  for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step) {
+    const TileCoord tc = decode_tile(p, t);
+    const uint32_t b2 = tc.batch % p.bdim2;
+    const uint32_t tmp = tc.batch / p.bdim2;
+    const uint32_t b1 = tmp % p.bdim1;
+    const uint32_t b0 = tmp / p.bdim1;
+    const int32_t c_b2 = static_cast<int32_t>(b2 * o.bmul[2]);
+    const int32_t c_b1 = static_cast<int32_t>(b1 * o.bmul[1]);
+    const int32_t c_b0 = static_cast<int32_t>(b0 * o.bmul[0]);
+    int32_t mn0;
+    if (IS_A) mn0 = static_cast<int32_t>(tc.mt * (PAIR ? 256u : 128u) + rank * 128u);
+    else if (PAIR) mn0 = static_cast<int32_t>(SWIGLU ? tc.nt * 128u : tc.nt * 256u + rank * 128u);
+    else mn0 = static_cast<int32_t>(tc.nt * kOutCols);
+    for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+      PROF_WAIT(wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code));
+      if (!ok) break;
+      const uint32_t bar = full0 + s * 8u;
+      if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes);
+      else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes);
+      const int32_t k0 = static_cast<int32_t>(kb * p.bk);
+      uint32_t dst = smem_operand + s * kStageBytes;
+      for (uint32_t i = 0; i < o.boxes; ++i, dst += o.box_bytes) {
+        const CUtensorMap* mp = map0;
+        uint32_t j = i;
+        if (!IS_A && SWIGLU && !PAIR && i >= o.boxes / 2) { mp = map1; j = i - o.boxes / 2; }
+        const int32_t mn = mn0 + static_cast<int32_t>(j * o.box_mn);
+        int32_t c0, c1, c2, c3, c4;
+        if (!o.mn_major) { c0 = k0; c1 = mn; c2 = c_b2; c3 = c_b1; c4 = c_b0; }
+        else if (!o.slab_dim) { c0 = mn; c1 = k0; c2 = c_b2; c3 = c_b1; c4 = c_b0; }
+        else { c0 = 0; c1 = k0; c2 = mn / static_cast<int32_t>(o.inner); c3 = c_b2; c4 = c_b1; }
+        if (PAIR) tma_load_5d_pair(dst, mp, bar, c0, c1, c2, c3, c4);
+        else tma_load_5d(dst, mp, bar, c0, c1, c2, c3, c4);
+      }
+      ++issued;
+      if (++s == kStages) { s = 0; ph ^= 1u; }
+    }
+  }
+  PROF_DUMP(IS_A ? 0 : 3);
+  if (*abort_flag && IS_A && rank == 0) {
+    // Let copies already issued land before this CTA's shared memory goes away.  CTA 0's
+    // `full` barriers count the bytes of both operands (and of both CTAs of a pair).
+    const uint32_t first = issued > static_cast<uint32_t>(kStages) ? issued - kStages : 0u;
+    for (uint32_t j = first; j < issued; ++j)
+      wait_drain(smem_u32(&tail->full[j % kStages]), (j / kStages) & 1u);
+  }
+}
+
 // -------------------------------------------------------------- the kernel
-template <int KIND, int BN, int OUT, bool SWIGLU>
+// PAIR = false: one CTA per 128 x BN tile.
+// PAIR = true : two CTAs on neighbouring SMs share a 256 x 256 tile through `cta_group::2`
+//   MMAs.  Each CTA stages its own 128 rows of A and its own 128 columns of B (two thirds of
+//   the L2->SM traffic of two 1-CTA tiles, and 32 KB stages so six fit), CTA 0 issues
+//   the MMAs, each CTA's TMEM receives its 128 rows x 256 columns of the accumulator and each
+//   CTA runs its own epilogue.  Loads are plain per-CTA TMA loads; CTA 0's commits signal
+//   `empty` / `tmem_full` in both CTAs.  With SWIGLU, CTA 0 stages the gate weights and CTA 1
+//   the up weights of the same 128 output columns.
+template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const TcParams p) {
-  using Cfg = TileCfg<BN>;
+  using Cfg = TileCfg<BN, PAIR>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kStageB = Cfg::kStageB;
+  constexpr int CG = PAIR ? 2 : 1;
   constexpr bool kIntAcc = (KIND == KIND_I8);
   constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
+  constexpr uint32_t kTileM = PAIR ? 256u : 128u;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -228,16 +335,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const uint32_t first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const uint32_t tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
   volatile uint32_t* abort_flag = &tail->abort_flag;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&tail->full[s]), 1);
-      mbar_init(smem_u32(&tail->empty[s]), 1);
+      mbar_init(smem_u32(&tail->full[s]), 2);   // one arrive(+tx) per operand producer
+      mbar_init(smem_u32(&tail->empty[s]), 1);  // one commit arrive (delivered to both CTAs of a pair)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tail->tmem_full[i]), 1);
-      mbar_init(smem_u32(&tail->tmem_empty[i]), 4);  // one arrive per epilogue warp
+      mbar_init(smem_u32(&tail->tmem_empty[i]), 4 * CG);  // one arrive per epilogue warp
     }
     mbar_init(smem_u32(&tail->drain), 1);
     tail->abort_flag = 0;
@@ -247,79 +357,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if constexpr (SWIGLU) prefetch_tensormap(&map_b2);
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(&tail->tmem_base), Cfg::kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<CG>(smem_u32(&tail->tmem_base), Cfg::kTmemCols);
+    tmem_relinquish<CG>();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tail->tmem_base);
-
   const uint32_t code_base = 0x80000000u | ((blockIdx.x & 0xFFFFu) << 4);
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ producer of A
+    if (lane == 0)
+      producer_role<BN, SWIGLU, PAIR, true>(p, p.a, &map_a, &map_a, tail, smem_a, rank, first_tile,
+                                            tile_step, code_base | 1u);
+    __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ producer of B
     if (lane == 0) {
-      const uint32_t stage_bytes = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
-      uint32_t s = 0, ph = 0, issued = 0;
-      bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
-        const TileCoord tc = decode_tile(p, t);
-        const uint32_t b2 = tc.batch % p.bdim2;
-        const uint32_t tmp = tc.batch / p.bdim2;
-        const uint32_t b1 = tmp % p.bdim1;
-        const uint32_t b0 = tmp / p.bdim1;
-        const int32_t m0 = static_cast<int32_t>(tc.mt * BM);
-        const int32_t n0 = static_cast<int32_t>(tc.nt * kOutCols);
-        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code_base | 1u);
-          if (!ok) break;
-          const uint32_t bar = smem_u32(&tail->full[s]);
-          mbar_arrive_expect_tx(bar, stage_bytes);
-          const int32_t k0 = static_cast<int32_t>(kb * p.bk);
-          uint32_t dst = smem_a + s * kStageA;
-          for (uint32_t i = 0; i < p.a_boxes; ++i, dst += p.a_box_bytes) {
-            const int32_t mn = m0 + static_cast<int32_t>(i * p.a_box_mn);
-            tma_load_5d(dst, &map_a, bar, p.a_mn_major ? mn : k0, p.a_mn_major ? k0 : mn,
-                        b2 * p.a_bmul[2], b1 * p.a_bmul[1], b0 * p.a_bmul[0]);
-          }
-          dst = smem_b + s * kStageB;
-          for (uint32_t i = 0; i < p.b_boxes; ++i, dst += p.b_box_bytes) {
-            const CUtensorMap* mp = &map_b;
-            uint32_t j = i;
-            if constexpr (SWIGLU) {
-              if (i >= p.b_boxes / 2) { mp = &map_b2; j = i - p.b_boxes / 2; }
-            }
-            const int32_t mn = n0 + static_cast<int32_t>(j * p.b_box_mn);
-            tma_load_5d(dst, mp, bar, p.b_mn_major ? mn : k0, p.b_mn_major ? k0 : mn,
-                        b2 * p.b_bmul[2], b1 * p.b_bmul[1], b0 * p.b_bmul[0]);
-          }
-          ++issued;
-          if (++s == kStages) { s = 0; ph ^= 1u; }
-        }
-      }
-      if (*abort_flag) {
-        // Let copies already issued into this CTA's shared memory land before exit.
-        const uint32_t first = issued > static_cast<uint32_t>(kStages) ? issued - kStages : 0u;
-        for (uint32_t j = first; j < issued; ++j)
-          wait_drain(smem_u32(&tail->full[j % kStages]), (j / kStages) & 1u);
-      }
+      const CUtensorMap* m0 = (PAIR && SWIGLU && rank == 1) ? &map_b2 : &map_b;
+      producer_role<BN, SWIGLU, PAIR, false>(p, p.b, m0, &map_b2, tail, smem_b, rank, first_tile,
+                                             tile_step, code_base | 5u);
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (CTA 0 of a pair)
+    if (lane == 0 && rank == 0) {
       uint32_t s = 0, ph = 0, lt = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++lt) {
+      PROF_DECL;
+#ifdef HODU_TC_PROFILE
+      long long prof_full = 0;
+#endif
+      for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step, ++lt) {
         const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
-        ok = wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
-                          code_base | 2u);
+        PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
+                               code_base | 2u));
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+#ifdef HODU_TC_PROFILE
+          const long long tw = clock64();
+#endif
           ok = wait_bounded(smem_u32(&tail->full[s]), ph, abort_flag, p.status, code_base | 3u);
+#ifdef HODU_TC_PROFILE
+          prof_full += clock64() - tw;
+#endif
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a16 = (smem_a + s * kStageA) >> 4;
@@ -327,31 +412,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {
             const uint64_t adesc =
-                (static_cast<uint64_t>(p.a_desc_hi) << 32) |
-                static_cast<uint64_t>(((a16 + k * p.a_kstep16) & 0x3FFFu) | p.a_desc_lo);
+                (static_cast<uint64_t>(p.a.desc_hi) << 32) |
+                static_cast<uint64_t>(((a16 + k * p.a.kstep16) & 0x3FFFu) | p.a.desc_lo);
             const uint64_t bdesc =
-                (static_cast<uint64_t>(p.b_desc_hi) << 32) |
-                static_cast<uint64_t>(((b16 + k * p.b_kstep16) & 0x3FFFu) | p.b_desc_lo);
-            umma<KIND, 1>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0u ? 1u : 0u);
+                (static_cast<uint64_t>(p.b.desc_hi) << 32) |
+                static_cast<uint64_t>(((b16 + k * p.b.kstep16) & 0x3FFFu) | p.b.desc_lo);
+            umma<KIND, CG>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0u ? 1u : 0u);
           }
-          umma_commit_1cta(smem_u32(&tail->empty[s]));  // frees the stage when the MMAs retire
+          // frees the stage (in both CTAs of a pair) when these MMAs retire
+          if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->empty[s]), 3);
+          else umma_commit_1cta(smem_u32(&tail->empty[s]));
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
-        umma_commit_1cta(smem_u32(&tail->tmem_full[acc]));
+        if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->tmem_full[acc]), 3);
+        else umma_commit_1cta(smem_u32(&tail->tmem_full[acc]));
       }
+      PROF_DUMP(1);
+#ifdef HODU_TC_PROFILE
+      if (blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2] = prof_full;
+#endif
       if (*abort_flag) {
-        umma_commit_1cta(smem_u32(&tail->drain));
+        if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->drain), 1);
+        else umma_commit_1cta(smem_u32(&tail->drain));
         wait_drain(smem_u32(&tail->drain), 0u);
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------ epilogue (warps 2..5)
     const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
     const uint32_t osz = OutBytes<OUT>::value;
+    const uint32_t tmem_empty0 =
+        PAIR ? mapa_shared(smem_u32(&tail->tmem_empty[0]), 0u) : smem_u32(&tail->tmem_empty[0]);
     uint32_t lt = 0;
-    for (uint32_t t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
+    for (uint32_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt) {
       const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
       bool ok = wait_bounded(smem_u32(&tail->tmem_full[acc]), acc_ph, abort_flag, p.status,
                              code_base | 4u);
@@ -359,7 +454,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!ok) break;
       tc_fence_after_sync();
       const TileCoord tc = decode_tile(p, t);
-      const uint32_t row = tc.mt * BM + q * 32u + lane;
+      const uint32_t row = tc.mt * kTileM + rank * 128u + q * 32u + lane;
       const uint32_t n0 = tc.nt * kOutCols;
       const bool row_ok = row < p.M;
       uint8_t* out_row = static_cast<uint8_t*>(p.out) +
@@ -406,15 +501,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tail->tmem_empty[acc]));
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster_addr(tmem_empty0 + acc * 8u);
+        else mbar_arrive(tmem_empty0 + acc * 8u);
+      }
     }
   }
 
+  // A CTA of a pair may not leave (or free TMEM) while its peer can still read its shared
+  // memory, signal its barriers or write its TMEM.
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
+    tmem_dealloc<CG>(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -435,6 +536,12 @@ __global__ void wait_timeout_probe_kernel(uint32_t* status, uint64_t limit_ns) {
 }
 
 // -------------------------------------------------------------- host side
+// HODU_B200_DEBUG=1 prints each tensor-core launch configuration to stderr.
+bool debug_enabled() {
+  static const bool on = [] { const char* e = getenv("HODU_B200_DEBUG"); return e && e[0] == '1'; }();
+  return on;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -455,6 +562,7 @@ EncodeTiledFn encode_fn() {
 
 struct OperandMap {
   bool mn_major = false;
+  bool slab_dim = false;
   uint32_t bmul[3] = {0, 0, 0};
   CUtensorMap map;
 };
@@ -522,13 +630,17 @@ int classify_operand(const Operand& op, int esize, int64_t rows, int64_t cols, b
   return -1;
 }
 
-// Builds the 5-D tensor map {inner, outer, batch2, batch1, batch0} of one operand.
-// rows/cols: logical matrix extents; `k_is_col` says whether K is the column
-// index (lhs) or the row index (rhs).  A K-major box is {128 B of K, tile_mn rows};
-// an MN-major box is {128 B of M/N, 128/esize rows of K} (one stage of K).
+// Builds the 5-D tensor map of one operand.  rows/cols: logical matrix extents; `k_is_col`
+// says whether K is the column index (lhs) or the row index (rhs).
+//   K-major : dims {K, MN, batch2, batch1, batch0}, box {128 B of K, tile_mn rows}.
+//   MN-major: dims {MN, K, batch2, batch1, batch0}, box {128 B of MN, 128/esize rows of K}:
+//             one box per 128-byte slab of the tile.
+//   MN-major with `slabs_per_box` > 1 (needs MN % (128/esize) == 0 and at most two batch dims):
+//             dims {128 B of MN, K, MN slabs, batch2, batch1}, box {128 B, K rows, slabs}: the
+//             whole tile in ONE box, laid out slab after slab exactly as separate boxes would be.
 const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_t cols,
                               bool k_is_col, const BatchDims& bd, const int64_t* bstride,
-                              uint32_t tile_mn /* rows of M/N per K-major box */, OperandMap* out) {
+                              uint32_t tile_mn, uint32_t slabs_per_box, OperandMap* out) {
   const int64_t mn = k_is_col ? rows : cols;
   const int64_t kk = k_is_col ? cols : rows;
   const int64_t s_mn = k_is_col ? op.stride_r : op.stride_c;
@@ -537,39 +649,48 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   if (base % 16 != 0) return "operand base address is not 16-byte aligned";
   if (mn > 0xFFFFFFFFll || kk > 0xFFFFFFFFll) return "extent exceeds 2^32";
 
-  auto stride_ok = [&](int64_t s) { return pitch_ok(s, esize); };
   const int cls = classify_operand(op, esize, rows, cols, k_is_col);
   if (cls < 0) return "neither matrix index is contiguous with a 16-byte-multiple pitch";
   const bool k_major = cls == 0;
   out->mn_major = !k_major;
+  const uint32_t inner_box = 128u / esize;  // 128 bytes: one swizzle row
+  out->slab_dim = !k_major && slabs_per_box > 1 && mn % inner_box == 0 && bd.size[0] == 1;
 
   const int64_t inner = k_major ? kk : mn;
   const int64_t outer = k_major ? mn : kk;
   int64_t pitch = k_major ? s_mn : s_k;  // elements between consecutive `outer` indices
-  if (outer == 1 || !stride_ok(pitch)) pitch = ((inner * esize + 15) / 16 * 16) / esize;
-  if (!stride_ok(pitch)) return "pitch is not a positive multiple of 16 bytes";
+  if (outer == 1 || !pitch_ok(pitch, esize)) pitch = ((inner * esize + 15) / 16 * 16) / esize;
+  if (!pitch_ok(pitch, esize)) return "pitch is not a positive multiple of 16 bytes";
 
   cuuint64_t dims[5] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), 1, 1, 1};
   cuuint64_t strides[4];
+  cuuint32_t box[5] = {inner_box, k_major ? tile_mn : inner_box, 1, 1, 1};
   strides[0] = static_cast<cuuint64_t>(pitch) * esize;
+  int first_batch_dim = 2;
+  if (out->slab_dim) {
+    dims[0] = inner_box;
+    dims[2] = static_cast<cuuint64_t>(mn / inner_box);
+    strides[1] = 128;
+    box[2] = slabs_per_box;
+    first_batch_dim = 3;
+  }
   cuuint64_t natural = strides[0] * dims[1];
-  for (int j = 0; j < 3; ++j) {  // j = 0 is the fastest-varying batch dim (slot 2)
+  for (int j = 0; first_batch_dim + j < 5; ++j) {  // j = 0 is the fastest-varying batch dim (slot 2)
     const int slot = kMaxBatchDims - 1 - j;
     const int64_t sz = bd.size[slot], bs = bstride[slot];
+    const int d = first_batch_dim + j;
     if (sz > 1 && bs != 0) {
-      if (!stride_ok(bs)) return "batch stride is not a positive multiple of 16 bytes";
-      dims[2 + j] = static_cast<cuuint64_t>(sz);
-      strides[1 + j] = static_cast<cuuint64_t>(bs) * esize;
+      if (!pitch_ok(bs, esize)) return "batch stride is not a positive multiple of 16 bytes";
+      dims[d] = static_cast<cuuint64_t>(sz);
+      strides[d - 1] = static_cast<cuuint64_t>(bs) * esize;
       out->bmul[slot] = 1;
     } else {
-      dims[2 + j] = 1;
-      strides[1 + j] = (natural + 15) / 16 * 16;
+      dims[d] = 1;
+      strides[d - 1] = (natural + 15) / 16 * 16;
       out->bmul[slot] = 0;
     }
-    natural = strides[1 + j] * dims[2 + j];
+    natural = strides[d - 1] * dims[d];
   }
-  const uint32_t inner_box = 128u / esize;  // 128 bytes: one swizzle row
-  cuuint32_t box[5] = {inner_box, k_major ? tile_mn : inner_box, 1, 1, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   const CUtensorMapDataType dt = esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
@@ -583,40 +704,69 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   return nullptr;
 }
 
-template <int KIND, int BN, int OUT, bool SWIGLU>
+template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR>
 int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
-                const TcParams& p, int device, int grid, cudaStream_t stream) {
-  using Cfg = TileCfg<BN>;
+                const TcParams& p, int device, int sm_count, cudaStream_t stream) {
+  using Cfg = TileCfg<BN, PAIR>;
   constexpr size_t smem = Cfg::kStages * (kStageA + Cfg::kStageB) + sizeof(SmemTail) + 1024;
-  static bool attr_set[kMaxDevices] = {false};
-  auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU>;
-  if (!attr_set[device]) {
+  static int max_ctas[kMaxDevices] = {0};  // CTAs (1-CTA form) or CTA pairs that can be resident
+  auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU, PAIR>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = PAIR ? 1 : 0;
+  if (max_ctas[device] == 0) {
     HODU_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)),
                   HODU_B200_ERR_LAUNCH);
-    attr_set[device] = true;
+    int n = PAIR ? sm_count / 2 : sm_count;
+    if (PAIR) {
+      cfg.gridDim = dim3(2, 1, 1);
+      int q = 0;
+      if (cudaOccupancyMaxActiveClusters(&q, kern, &cfg) == cudaSuccess && q >= 1) n = q;
+      else cudaGetLastError();
+    }
+    max_ctas[device] = n > 0 ? n : 1;
   }
-  kern<<<grid, kThreads, smem, stream>>>(ma, mb, mb2, p);
-  HODU_CUDA_TRY(cudaGetLastError(), HODU_B200_ERR_LAUNCH);
+  const int units = static_cast<int>(p.num_tiles < static_cast<uint32_t>(max_ctas[device]) ? p.num_tiles : max_ctas[device]);
+  cfg.gridDim = dim3(PAIR ? 2 * units : units, 1, 1);
+  if (debug_enabled())
+    fprintf(stderr, "[hodu_b200] gemm_tc %s: %u tiles of %dx%d, grid %u, %zu B smem, A %s x%u, B %s x%u%s\n",
+            PAIR ? "pair" : "1-CTA", p.num_tiles, PAIR ? 256 : 128, SWIGLU ? BN / 2 : BN, cfg.gridDim.x, smem,
+            p.a.mn_major ? "M-major" : "K-major", p.a.boxes, p.b.mn_major ? "N-major" : "K-major", p.b.boxes,
+            p.b.slab_dim ? " (slab dim)" : "");
+  HODU_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, mb2, p), HODU_B200_ERR_LAUNCH);
   count_launch();
   return 0;
 }
 
 template <int KIND, int OUT, bool SWIGLU>
-int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
-              const TcParams& p, int device, int grid, cudaStream_t stream) {
+int launch_shape(int bn, bool pair, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+                 const TcParams& p, int device, int sm_count, cudaStream_t stream) {
+  if (pair) return launch_inst<KIND, 256, OUT, SWIGLU, true>(ma, mb, mb2, p, device, sm_count, stream);
   if constexpr (SWIGLU) {
-    return launch_inst<KIND, 256, OUT, true>(ma, mb, mb2, p, device, grid, stream);
+    return launch_inst<KIND, 256, OUT, true, false>(ma, mb, mb2, p, device, sm_count, stream);
   } else {
     switch (bn) {
-      case 256: return launch_inst<KIND, 256, OUT, false>(ma, mb, mb2, p, device, grid, stream);
-      case 128: return launch_inst<KIND, 128, OUT, false>(ma, mb, mb2, p, device, grid, stream);
-      default: return launch_inst<KIND, 64, OUT, false>(ma, mb, mb2, p, device, grid, stream);
+      case 256: return launch_inst<KIND, 256, OUT, false, false>(ma, mb, mb2, p, device, sm_count, stream);
+      case 128: return launch_inst<KIND, 128, OUT, false, false>(ma, mb, mb2, p, device, sm_count, stream);
+      default: return launch_inst<KIND, 64, OUT, false, false>(ma, mb, mb2, p, device, sm_count, stream);
     }
   }
 }
 
 }  // namespace
+
+#ifdef HODU_TC_PROFILE
+extern "C" int hodu_b200_debug_read_prof(unsigned long long* out64) {
+  return cudaMemcpyFromSymbol(out64, g_tc_prof, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t limit_ms) {
   wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(st->status, static_cast<uint64_t>(limit_ms) * 1000000ull);
@@ -642,15 +792,22 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   BatchDims bd;
   if (!collapse_batch(pb, &bd)) { *why = "more than three independent batch dims"; return 1; }
   if (pb.batches > 0x7FFFFFFFll) { *why = "too many batches"; return 1; }
-
-  // Tile width: the widest tile that still gives every SM a tile; a tile is never
-  // more than twice as wide as N.  An 8-bit N-contiguous rhs needs >= 128 columns
-  // (one 128-byte swizzle row holds 128 of its elements).
-  const int64_t tiles_m = (pb.M + BM - 1) / BM;
   const int b_cls = classify_operand(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false);
   if (b_cls < 0) { *why = "rhs: neither matrix index is contiguous with a 16-byte-multiple pitch"; return 1; }
+
+  // Tile shape.  A CTA pair per 256 x 256 tile once there are enough such tiles to occupy the
+  // pairs; otherwise one CTA per 128 x BN tile with the widest BN that still gives every SM a
+  // tile (never more than twice as wide as N).  An 8-bit N-contiguous rhs needs BN >= 128:
+  // one 128-byte swizzle row holds 128 of its elements.
+  const int forced = forced_path();
+  const int out_cols_pair = pb.swiglu ? 128 : 256;
+  const int64_t pair_tiles = ((pb.M + 255) / 256) * ((pb.N + out_cols_pair - 1) / out_cols_pair) * pb.batches;
+  bool use_pair = pb.M > 128 && (pb.swiglu || pb.N > 128) && pair_tiles * 2 >= st->sm_count / 2;
+  if (forced == HODU_B200_PATH_TENSOR_1CTA) use_pair = false;
+  if (forced == HODU_B200_PATH_TENSOR_2CTA) use_pair = true;
+  const int64_t tiles_m = use_pair ? (pb.M + 255) / 256 : (pb.M + BM - 1) / BM;
   int bn = 256;
-  if (!pb.swiglu) {
+  if (!pb.swiglu && !use_pair) {
     const int min_bn = (b_cls == 1 && esize == 1) ? 128 : 64;
     for (int c = 256; c >= min_bn; c >>= 1) {
       if (c > min_bn && pb.N <= c / 2) continue;
@@ -658,22 +815,28 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
       if (tiles_m * ((pb.N + c - 1) / c) * pb.batches >= st->sm_count) break;
     }
   }
-  const int out_cols = pb.swiglu ? bn / 2 : bn;
+  const int out_cols = pb.swiglu ? bn / 2 : bn;       // output columns per tile
   const int64_t tiles_n = (pb.N + out_cols - 1) / out_cols;
   const int64_t num_tiles = tiles_m * tiles_n * pb.batches;
   if (num_tiles > 0x7FFFFFFFll) { *why = "too many tiles"; return 1; }
+  // Columns of B one CTA stages per k-block, and how many TMA boxes bring them in.
+  const uint32_t b_cols_staged = use_pair ? 128u : static_cast<uint32_t>(bn);
+  const uint32_t b_sources = (pb.swiglu && !use_pair) ? 2u : 1u;   // gate and up halves from two maps
+  const uint32_t b_cols_per_box = b_cols_staged / b_sources;
+  const uint32_t mn_per_slab = 128u / esize;
 
   OperandMap oa, ob, ob2;
-  const char* err = build_operand_map(pb.a, esize, pb.M, pb.K, /*k_is_col=*/true, bd, bd.a_stride, BM, &oa);
+  const char* err = build_operand_map(pb.a, esize, pb.M, pb.K, /*k_is_col=*/true, bd, bd.a_stride, BM,
+                                      BM / mn_per_slab, &oa);
   if (err) { *why = err; return 1; }
-  err = build_operand_map(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false, bd, bd.b_stride,
-                          static_cast<uint32_t>(out_cols), &ob);
+  err = build_operand_map(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false, bd, bd.b_stride, b_cols_per_box,
+                          b_cols_per_box / mn_per_slab, &ob);
   if (err) { *why = err; return 1; }
   if (pb.swiglu) {
-    err = build_operand_map(pb.b2, esize, pb.K, pb.N, false, bd, bd.b2_stride,
-                            static_cast<uint32_t>(out_cols), &ob2);
+    err = build_operand_map(pb.b2, esize, pb.K, pb.N, false, bd, bd.b2_stride, b_cols_per_box,
+                            b_cols_per_box / mn_per_slab, &ob2);
     if (err) { *why = err; return 1; }
-    if (ob2.mn_major != ob.mn_major) { *why = "gate and up weights differ in layout"; return 1; }
+    if (ob2.mn_major != ob.mn_major || ob2.slab_dim != ob.slab_dim) { *why = "gate and up weights differ in layout"; return 1; }
     for (int j = 0; j < 3; ++j)
       if (ob2.bmul[j] != ob.bmul[j]) { *why = "gate and up weights differ in batch broadcast"; return 1; }
   } else {
@@ -686,35 +849,34 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   p.num_tiles = static_cast<uint32_t>(num_tiles);
   p.bk = 128u / esize;
   p.k_blocks = static_cast<uint32_t>((pb.K + p.bk - 1) / p.bk);
-  p.group_m = 16;
+  p.group_m = use_pair ? 8 : 16;
   p.bdim1 = static_cast<uint32_t>(bd.size[1]); p.bdim2 = static_cast<uint32_t>(bd.size[2]);
-  for (int j = 0; j < 3; ++j) { p.a_bmul[j] = oa.bmul[j]; p.b_bmul[j] = ob.bmul[j]; }
-  p.a_mn_major = oa.mn_major; p.b_mn_major = ob.mn_major;
 
-  const uint32_t slab_bytes = 128u * p.bk;          // MN-major box: bk rows of 128 bytes
-  const uint32_t mn_per_slab = 128u / esize;
+  const uint32_t slab_bytes = 128u * p.bk;          // MN-major slab: bk rows of 128 bytes
   const uint32_t kstep_rows = 32u / esize;          // K elements one MMA consumes
   const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128B swizzle
-  if (oa.mn_major) {
-    p.a_boxes = BM / mn_per_slab; p.a_box_bytes = slab_bytes; p.a_box_mn = mn_per_slab;
-    p.a_desc_lo = (slab_bytes >> 4) << 16; p.a_kstep16 = (kstep_rows * 128u) >> 4;
-  } else {
-    p.a_boxes = 1; p.a_box_bytes = kStageA; p.a_box_mn = BM;
-    p.a_desc_lo = 1u << 16; p.a_kstep16 = 2;
-  }
-  if (ob.mn_major) {
-    p.b_boxes = bn / mn_per_slab; p.b_box_bytes = slab_bytes; p.b_box_mn = mn_per_slab;
-    p.b_desc_lo = (slab_bytes >> 4) << 16; p.b_kstep16 = (kstep_rows * 128u) >> 4;
-  } else {
-    p.b_boxes = pb.swiglu ? 2 : 1; p.b_box_bytes = static_cast<uint32_t>(out_cols) * 128u;
-    p.b_box_mn = static_cast<uint32_t>(out_cols);
-    p.b_desc_lo = 1u << 16; p.b_kstep16 = 2;
-  }
-  p.a_desc_hi = desc_hi; p.b_desc_hi = desc_hi;
+  auto fill = [&](OperandLoad& o, const OperandMap& m, uint32_t mn_staged, uint32_t sources) {
+    o.mn_major = m.mn_major; o.slab_dim = m.slab_dim; o.inner = mn_per_slab;
+    for (int j = 0; j < 3; ++j) o.bmul[j] = m.bmul[j];
+    o.desc_hi = desc_hi;
+    if (m.mn_major) {
+      const uint32_t slabs = mn_staged / mn_per_slab;
+      if (m.slab_dim) { o.boxes = sources; o.box_bytes = slab_bytes * (slabs / sources); o.box_mn = mn_staged / sources; }
+      else { o.boxes = slabs; o.box_bytes = slab_bytes; o.box_mn = mn_per_slab; }
+      o.desc_lo = (slab_bytes >> 4) << 16; o.kstep16 = (kstep_rows * 128u) >> 4;
+    } else {
+      o.boxes = sources; o.box_mn = mn_staged / sources; o.box_bytes = o.box_mn * 128u;
+      o.desc_lo = 1u << 16; o.kstep16 = 2;
+    }
+  };
+  fill(p.a, oa, BM, 1);
+  fill(p.b, ob, b_cols_staged, b_sources);
+  // SwiGLU without the slab dimension walks gate slabs then up slabs: the producer switches
+  // maps at boxes / 2, which needs an even box count -- true for every case above.
   const uint32_t c_fmt = kind == KIND_I8 ? 2u : 1u;
   p.idesc = (c_fmt << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
             (static_cast<uint32_t>(oa.mn_major) << 15) | (static_cast<uint32_t>(ob.mn_major) << 16) |
-            (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+            (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>((use_pair ? 256 : BM) >> 4) << 24);
   p.alpha = pb.alpha;
   p.swiglu_flags = pb.swiglu_flags;
   p.ldc = static_cast<unsigned long long>(pb.N);
@@ -727,10 +889,9 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
 
   int device = 0;
   cudaGetDevice(&device);
-  const int grid = static_cast<int>(num_tiles < st->sm_count ? num_tiles : st->sm_count);
 
 #define HODU_TC(KIND, OUTE, SW) \
-  return launch_bn<KIND, OUTE, SW>(bn, oa.map, ob.map, ob2.map, p, device, grid, stream)
+  return launch_shape<KIND, OUTE, SW>(bn, use_pair, oa.map, ob.map, ob2.map, p, device, st->sm_count, stream)
   if (pb.swiglu) {
     if (kind != KIND_F16) { *why = "SwiGLU epilogue exists for bf16/f16 only"; return 1; }
     if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F16, OUT_BF16, true);

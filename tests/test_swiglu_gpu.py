@@ -49,7 +49,7 @@ def test_fused_hidden_matches_oracle(dt, weights_as_linear, flags):
             lg = lu = Layout.from_shape((k, n))
         want = O.swiglu_hidden(O.widen(xb, dt), O.widen(gb, dt), O.widen(ub, dt), dt,
                                round_each_op=(flags == _lib.SWIGLU_ROUND_EACH_OP))
-        wf = O.widen(want, dt)
+        wf = O.widen(want, dt).reshape(-1)
         for path in (_lib.PATH_TENSOR, _lib.PATH_SIMT):
             got = run_swiglu(xb, gs, us, lx, lg, lu, dt, flags, path)
             assert O.rel_err(O.widen(got, dt), wf) <= 1e-2
