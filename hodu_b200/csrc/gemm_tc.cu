@@ -3,12 +3,14 @@
 // `hodu_cuda_matmul_*` / `hodu_cuda_dot_*`
 // (crates/hodu_cuda_kernels/kernels/ops_matrix.cu:9-102,104-165).
 //
-// Shape of one CTA (192 threads, one CTA per SM, persistent over output tiles):
-//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a ring of stages
+// Shape of one CTA (224 threads, one CTA per SM, persistent over output tiles):
+//   warp 0      TMA producer of A: 128-byte-swizzled operand tiles into a ring of stages
+//   warp 6      TMA producer of B (its own barrier arrive, so neither operand waits on the other)
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane)
 //   warps 2..5  epilogue: tcgen05.ld of the accumulator, scale/convert, global store
 // The accumulator tile (128 x BN, f32 or s32) lives in TMEM and is double buffered,
-// so the epilogue of tile i overlaps the main loop of tile i+1.
+// so the epilogue of tile i overlaps the main loop of tile i+1.  Large problems run as
+// CTA pairs on 256 x 256 tiles (cta_group::2), see gemm_tc_kernel.
 //
 // Operand layouts: each of A and B may be K-major (K contiguous) or MN-major
 // (M resp. N contiguous); both are described to the tensor core through the
@@ -45,7 +47,7 @@ enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, 
 // Stage ring per CTA.  PAIR: each CTA of the pair stages 128 columns of B.
 template <int BN, bool PAIR> struct TileCfg {
   static constexpr int kStageB = PAIR ? 128 * 128 : BN * 128;
-  static constexpr int kStages = PAIR ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int kStages = PAIR ? 7 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
 };
 
@@ -274,6 +276,14 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
       PROF_WAIT(wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code));
       if (!ok) break;
       const uint32_t bar = full0 + s * 8u;
+#ifdef HODU_TC_PROFILE
+      if (p.out_vec_ok & 2u) {  // experiment: no loads at all, the MMAs run on whatever is in smem
+        if (!PAIR || rank == 0) mbar_arrive(smem_u32(&tail->full[s]));
+        ++issued;
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+        continue;
+      }
+#endif
       if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes);
       else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes);
       const int32_t k0 = static_cast<int32_t>(kb * p.bk);
@@ -407,6 +417,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #endif
           if (!ok) break;
           tc_fence_after_sync();
+#ifdef HODU_TC_PROFILE
+          if (p.out_vec_ok & 4u) {  // experiment: loads only, no MMAs
+            mbar_arrive(smem_u32(&tail->empty[s]));
+            if (PAIR) mbar_arrive_cluster_addr(mapa_shared(smem_u32(&tail->empty[s]), 1u));
+            if (++s == kStages) { s = 0; ph ^= 1u; }
+            continue;
+          }
+#endif
           const uint32_t a16 = (smem_a + s * kStageA) >> 4;
           const uint32_t b16 = (smem_b + s * kStageB) >> 4;
 #pragma unroll
@@ -886,6 +904,9 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   const int osz = dtype_size(pb.out_dtype);
   p.out_vec_ok = (reinterpret_cast<uintptr_t>(pb.out) % 16 == 0 && (pb.N * osz) % 16 == 0 &&
                   (p.out_batch_stride * osz) % 16 == 0) ? 1u : 0u;
+#ifdef HODU_TC_PROFILE
+  if (const char* e = getenv("HODU_TC_EXPERIMENT")) p.out_vec_ok |= static_cast<uint32_t>(atoi(e)) & 6u;
+#endif
 
   int device = 0;
   cudaGetDevice(&device);

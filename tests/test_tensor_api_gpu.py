@@ -50,7 +50,7 @@ def test_rank_dispatch_follows_the_reference():
     with pytest.raises(HoduError):
         A.matmul(Tensor.from_torch(torch.zeros(128, 8, device=DEV)))  # dtype mismatch
     with pytest.raises(HoduError):
-        bf16_tensor(a4).matmul(bf16_tensor(rng.standard_normal((4, 128, 8)).astype(np.float32)))
+        bf16_tensor(a4).matmul(bf16_tensor(rng.standard_normal((5, 4, 128, 8)).astype(np.float32)))  # 2 vs 5
 
 
 def test_linear_forward_uses_the_transposed_view():
