@@ -24,7 +24,8 @@ DeviceState g_state[kMaxDevices];
 
 // Tensor-core path only above this much work; below it one CUDA-core CTA wave
 // finishes sooner than the TMA/TMEM pipeline fills.
-constexpr long long kTensorMinWork = 1ll << 21;  // M*N*K*batches
+constexpr long long kTensorMinWork = 1ll << 21;     // M*N*K*batches
+constexpr long long kTensorMinWorkF32 = 1ll << 24;  // f32 pays two operand-split launches first
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -201,10 +202,12 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   const long long work = static_cast<long long>(pb.M) * pb.N * pb.K * pb.batches;
   const bool forced_tc = forced == HODU_B200_PATH_TENSOR || forced == HODU_B200_PATH_TENSOR_1CTA ||
                          forced == HODU_B200_PATH_TENSOR_2CTA;
-  const bool want_tc = forced_tc || (forced == HODU_B200_PATH_AUTO && work >= kTensorMinWork);
+  const long long min_work = pb.in_dtype == HODU_DTYPE_F32 ? kTensorMinWorkF32 : kTensorMinWork;
+  const bool want_tc = forced_tc || (forced == HODU_B200_PATH_AUTO && work >= min_work);
   if (want_tc) {
     const char* why = "";
-    const int r = launch_gemm_tc(pb, st, stream, &why);
+    const int r = pb.in_dtype == HODU_DTYPE_F32 ? launch_gemm_f32(pb, st, stream, &why)
+                                                : launch_gemm_tc(pb, st, stream, &why);
     if (r == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
     if (r < 0) return r;
     if (forced_tc) return fail(HODU_B200_ERR_INVALID_INPUT, "tensor-core path refused: %s", why);

@@ -81,6 +81,7 @@ struct Problem {
   uint32_t swiglu_flags = 0;
   void* out = nullptr;   // contiguous [batches, M, N]
   float alpha = 1.0f;    // scale_lhs * scale_rhs
+  bool f32_presplit = false;  // f32 operands already in the three-segment TF32 split form (gemm_f32.cu)
 };
 
 // Generic strided CUDA-core kernel: any layout, every supported dtype pair.
@@ -88,6 +89,13 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream);
 // tcgen05 kernel. Returns 1 if the layout cannot be described to TMA (nothing
 // launched, `why` says which rule failed), 0 when launched, <0 on error.
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// f32 on the tensor cores through split TF32 operands held in scratch memory (gemm_f32.cu).
+// Return convention as launch_gemm_tc.  `launch_gemm_f32` takes the scratch from the
+// stream-ordered allocator; `launch_gemm_f32_split` uses the scratch it is given.
+size_t gemm_f32_scratch_bytes(const Problem& pb);
+int launch_gemm_f32(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t stream, void* scratch,
+                          size_t scratch_bytes, const char** why);
 // One tiny kernel whose only wait can never be satisfied; it gives up after limit_ms.
 int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t limit_ms);
 // Parsers of the reference's wire formats and the path chooser (api.cu).

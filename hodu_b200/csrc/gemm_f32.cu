@@ -1,0 +1,187 @@
+// f32 matmul on the tensor cores: C = A . B computed as three TF32 products of split
+// operands (A = Ahi + Alo, B = Bhi + Blo; C ~= Ahi.Bhi + Ahi.Blo + Alo.Bhi, f32 accumulate),
+// which keeps ~21 bits per product -- inside the 1e-4 bar of the f32 configuration, where one
+// plain TF32 product (10-bit mantissa) is not.  The reference computes f32 products on CUDA
+// cores (crates/hodu_cuda_kernels/kernels/ops_matrix.cu:9-102); on B200 the same result comes
+// ~10x sooner this way.
+//
+// Step 1 (this file): one pass over each operand writes its split form into SCRATCH memory,
+//   A' = [Ahi | Ahi | Alo] (M x 3K) and B'^T = [Bhi | Blo | Bhi] (N x 3K), both K-contiguous with
+//   a 16-byte-multiple pitch.  (With an M- or N-contiguous operand kind::tf32 returned zeros on
+//   this hardware, so the split pass transposes through shared memory where needed; reads and
+//   writes both stay coalesced.)  Any strides and offsets are accepted on the way in;
+//   broadcast batch dims are split once.
+// Step 2: the tcgen05 kernel (gemm_tc.cu, kind::tf32) multiplies A' [M,3K] by B' [3K,N].
+// The scratch comes from the stream-ordered allocator on the caller's stream, so concurrent
+// calls on different streams never share it.
+#include "common.cuh"
+
+namespace hodu_b200 {
+namespace {
+
+struct SplitParams {
+  const float* src;
+  float* dst;
+  long long mn, k;               // logical [mn, k] view of one matrix (mn = M for lhs, N for rhs)
+  long long s_mn, s_k;           // source element strides of those two indices
+  long long nb;                  // physical (non-broadcast) batch count
+  int nbd;                       // physical batch dims (<= 3)
+  long long bshape[3], bstride[3];
+  long long pitch;               // destination pitch in elements (>= 3k, multiple of 4)
+  long long mat_elems;           // destination elements per matrix (pitch * mn)
+  int lo_part;                   // which of the three K segments holds the low part (2 lhs, 1 rhs)
+  long long tiles_mn, tiles_k;
+};
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+// 32 x 32 tiles, 256 threads (32 x 8).  The source is read along whichever of its two indices
+// is contiguous; the destination is always written along k.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitParams p) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long per = p.tiles_mn * p.tiles_k;
+  const bool k_fast = (p.s_k == 1) || (p.s_mn != 1);
+  for (long long t = blockIdx.x; t < per * p.nb; t += gridDim.x) {
+    const long long b = t / per, r = t - b * per;
+    const long long mn0 = (r / p.tiles_k) * 32, k0 = (r % p.tiles_k) * 32;
+    long long boff = 0, rem = b;
+    for (int d = p.nbd - 1; d >= 0; --d) { boff += (rem % p.bshape[d]) * p.bstride[d]; rem /= p.bshape[d]; }
+    const float* src = p.src + boff;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i_mn = k_fast ? ty + 8 * j : tx;
+      const int i_k = k_fast ? tx : ty + 8 * j;
+      const long long g_mn = mn0 + i_mn, g_k = k0 + i_k;
+      tile[i_mn][i_k] = (g_mn < p.mn && g_k < p.k) ? src[g_mn * p.s_mn + g_k * p.s_k] : 0.0f;
+    }
+    __syncthreads();
+    float* dst = p.dst + b * p.mat_elems;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long g_mn = mn0 + ty + 8 * j, g_k = k0 + tx;
+      if (g_mn < p.mn && g_k < p.k) {
+        const float x = tile[ty + 8 * j][tx];
+        const float hi = tf32_round(x), lo = tf32_round(x - hi);  // both rounded to nearest: no truncation bias in the MMA
+        float* row = dst + g_mn * p.pitch + g_k;
+        row[0] = hi;
+        row[p.k] = (p.lo_part == 1) ? lo : hi;
+        row[2 * p.k] = (p.lo_part == 2) ? lo : hi;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+struct SplitPlan {
+  SplitParams sp;
+  size_t bytes;
+  Operand out;  // the split operand as the tensor-core problem sees it (ptr filled in later)
+};
+
+// Plans the split of one operand of `pb`; returns false if it has more than three
+// non-broadcast batch dims.
+bool plan_split(const Problem& pb, const Operand& op, bool is_lhs, SplitPlan* plan) {
+  SplitParams& sp = plan->sp;
+  sp = SplitParams{};
+  sp.mn = is_lhs ? pb.M : pb.N;
+  sp.k = pb.K;
+  sp.s_mn = is_lhs ? op.stride_r : op.stride_c;
+  sp.s_k = is_lhs ? op.stride_c : op.stride_r;
+  sp.lo_part = is_lhs ? 2 : 1;
+  sp.pitch = (3 * sp.k + 3) / 4 * 4;
+  sp.mat_elems = sp.pitch * sp.mn;
+  sp.tiles_mn = (sp.mn + 31) / 32;
+  sp.tiles_k = (sp.k + 31) / 32;
+  sp.nb = 1; sp.nbd = 0;
+  plan->out = Operand{};
+  long long dense = sp.mat_elems;
+  // physical batch dims, innermost last; broadcast dims keep stride 0 in the new operand
+  int dims[16], n = 0;
+  for (int d = 0; d < pb.batch_ndim; ++d)
+    if (pb.batch_shape[d] > 1 && op.bstride[d] != 0) dims[n++] = d;
+  if (n > 3) return false;
+  for (int j = n - 1; j >= 0; --j) {
+    const int d = dims[j];
+    plan->out.bstride[d] = dense;
+    dense *= pb.batch_shape[d];
+  }
+  for (int j = 0; j < n; ++j) {
+    sp.bshape[j] = pb.batch_shape[dims[j]];
+    sp.bstride[j] = op.bstride[dims[j]];
+    sp.nb *= sp.bshape[j];
+  }
+  sp.nbd = n;
+  plan->bytes = static_cast<size_t>(dense) * sizeof(float);
+  plan->out.offset = 0;
+  // K-contiguous: lhs [M, 3K] has strides (pitch, 1); rhs [3K, N] has strides (1, pitch)
+  plan->out.stride_r = is_lhs ? sp.pitch : 1;
+  plan->out.stride_c = is_lhs ? 1 : sp.pitch;
+  return true;
+}
+
+int run_split(const SplitPlan& plan, const void* src, int64_t src_offset, float* dst, DeviceState* st,
+              cudaStream_t stream) {
+  SplitParams sp = plan.sp;
+  sp.src = static_cast<const float*>(src) + src_offset;
+  sp.dst = dst;
+  long long blocks = sp.tiles_mn * sp.tiles_k * sp.nb;
+  const long long cap = static_cast<long long>(st->sm_count) * 32;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) return 0;
+  split_tf32_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sp);
+  HODU_CUDA_TRY(cudaGetLastError(), HODU_B200_ERR_LAUNCH);
+  count_launch();
+  return 0;
+}
+
+}  // namespace
+
+size_t gemm_f32_scratch_bytes(const Problem& pb) {
+  SplitPlan a, b;
+  if (!plan_split(pb, pb.a, true, &a) || !plan_split(pb, pb.b, false, &b)) return 0;
+  return ((a.bytes + 255) / 256 * 256) + b.bytes;
+}
+
+int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t stream, void* scratch,
+                          size_t scratch_bytes, const char** why) {
+  static const char* none = "";
+  *why = none;
+  if (pb.in_dtype != HODU_DTYPE_F32 || pb.out_dtype != HODU_DTYPE_F32 || pb.swiglu) { *why = "not an f32 product"; return 1; }
+  if (st->cc_major != 10) { *why = "device is not sm_100"; return 1; }
+  if (3 * pb.K > 0x7FFFFFFFll) { *why = "K too large"; return 1; }
+  SplitPlan a, b;
+  if (!plan_split(pb, pb.a, true, &a) || !plan_split(pb, pb.b, false, &b)) { *why = "more than three batch dims"; return 1; }
+  const size_t a_bytes = (a.bytes + 255) / 256 * 256;
+  if (a_bytes + b.bytes > scratch_bytes) { *why = "scratch too small"; return 1; }
+  float* da = static_cast<float*>(scratch);
+  float* db = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + a_bytes);
+  int r = run_split(a, pb.a.ptr, pb.a.offset, da, st, stream);
+  if (r) return r;
+  r = run_split(b, pb.b.ptr, pb.b.offset, db, st, stream);
+  if (r) return r;
+  Problem q = pb;
+  q.K = 3 * pb.K;
+  q.a = a.out; q.a.ptr = da;
+  q.b = b.out; q.b.ptr = db;
+  q.f32_presplit = true;
+  return launch_gemm_tc(q, st, stream, why);
+}
+
+// Allocates the scratch on `stream` (stream-ordered pool), runs the split product, frees it.
+int launch_gemm_f32(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
+  const size_t bytes = gemm_f32_scratch_bytes(pb);
+  if (bytes == 0) { *why = "more than three batch dims"; return 1; }
+  void* scratch = nullptr;
+  HODU_CUDA_TRY(cudaMallocAsync(&scratch, bytes, stream), HODU_B200_ERR_MEMORY);
+  const int r = launch_gemm_f32_split(pb, st, stream, scratch, bytes, why);
+  const cudaError_t e = cudaFreeAsync(scratch, stream);
+  if (r == 0 && e != cudaSuccess) return fail(HODU_B200_ERR_MEMORY, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
+  return r;
+}
+
+}  // namespace hodu_b200

@@ -802,6 +802,9 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
     case HODU_DTYPE_F16: kind = KIND_F16; esize = 2; fmt = 0; break;
     case HODU_DTYPE_F8E4M3: kind = KIND_F8; esize = 1; fmt = 0; break;
     case HODU_DTYPE_I8: kind = KIND_I8; esize = 1; fmt = 1; break;
+    case HODU_DTYPE_F32:
+      if (!pb.f32_presplit) { *why = "f32 reaches the tensor cores only through the TF32 split (gemm_f32.cu)"; return 1; }
+      kind = KIND_TF32; esize = 4; fmt = 2; break;
     default: *why = "input dtype has no tensor-core kernel"; return 1;
   }
   if (st->cc_major != 10) { *why = "device is not sm_100"; return 1; }
@@ -923,6 +926,8 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
     if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F16, OUT_BF16, false);
     if (pb.out_dtype == HODU_DTYPE_F16) HODU_TC(KIND_F16, OUT_F16, false);
     if (pb.out_dtype == HODU_DTYPE_F32) HODU_TC(KIND_F16, OUT_F32, false);
+  } else if (kind == KIND_TF32) {
+    if (pb.out_dtype == HODU_DTYPE_F32) HODU_TC(KIND_TF32, OUT_F32, false);
   } else if (kind == KIND_F8) {
     if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F8, OUT_BF16, false);
     if (pb.out_dtype == HODU_DTYPE_F16) HODU_TC(KIND_F8, OUT_F16, false);

@@ -136,13 +136,37 @@ def test_batched_broadcast(lshape, rshape, in_dt, out_dt, as_views):
     want = O.matmul(a, b, md, in_dt, out_dt)
     esize = np.dtype(O.NP_STORAGE[in_dt]).itemsize
     tma_ok = all((d * esize) % 16 == 0 for d in (lshape[-1], rshape[-1]))  # row pitches TMA can take
-    paths = [SIMT] if (in_dt == O.F32 or not tma_ok) else [SIMT, TENSOR]
+    paths = [SIMT, TENSOR] if (tma_ok or in_dt == O.F32) else [SIMT]  # the f32 path re-lays its operands
     for path in paths:
         got, taken = gpu_matmul(a, b, md, in_dt, out_dt, path=path)
         assert taken == path
         check_close(got, want, out_dt, TOL.get(in_dt, 0))
     if int(np.prod(out_l.shape)) * lshape[-1] < 300000:
         check_close(want, O.matmul_c(a, b, md, in_dt, out_dt), out_dt, TOL.get(in_dt, 0))
+
+
+@pytest.mark.parametrize("a_c,b_c", [("c", "c"), ("c", "r"), ("r", "c"), ("r", "r")])
+def test_f32_on_tensor_cores_keeps_f32_accuracy(a_c, b_c):
+    """Three TF32 products of split operands: far inside the 1e-4 bar (one plain TF32 product
+    would sit near 1e-3), for any strides, offsets and odd extents."""
+    rng = np.random.default_rng(31)
+    for (m, k, n) in [(512, 1024, 768), (130, 37, 29), (257, 515, 130), (1, 300, 64)]:
+        a, la = operand(rng, O.F32, m, k, a_c)
+        b, lb = operand(rng, O.F32, k, n, b_c)
+        md = dot_metadata(la, lb)
+        for path in (TENSOR, _lib.PATH_TENSOR_2CTA):
+            got, taken = gpu_matmul(a, b, md, O.F32, is_dot=True, path=path)
+            assert taken == TENSOR
+            want = np.matmul(O._strided(a.reshape(-1), la.shape, la.strides, 0).astype(np.float64),
+                             O._strided(b.reshape(-1), lb.shape, lb.strides, 0).astype(np.float64))
+            assert O.rel_err(got, want.reshape(-1)) <= 2e-5
+        assert O.rel_err(got, O.matmul(a, b, md, O.F32, is_dot=True)) <= 1e-4   # the reference's sgemm
+    # padded pitch + element offset that no TMA map could take directly
+    a = rand_storage(rng, O.F32, (5 + 70 * 67,))
+    b = rand_storage(rng, O.F32, (3 + 64 * 131,))
+    md = dot_metadata(Layout((70, 64), (67, 1), 5), Layout((64, 130), (131, 1), 3))
+    got, _ = gpu_matmul(a, b, md, O.F32, is_dot=True, path=TENSOR)
+    assert O.rel_err(got, O.matmul(a, b, md, O.F32, is_dot=True)) <= 1e-5
 
 
 def test_offsets_on_tensor_path():
@@ -173,10 +197,13 @@ def test_auto_path_selection_and_refusal():
     with pytest.raises(CudaKernelError) as e:
         gpu_matmul(a, b, md, O.BF16, is_dot=True, path=TENSOR)
     assert e.value.kind == "invalid input" and "tensor-core path refused" in str(e.value)
-    # f32 has no tensor-core kernel
-    a, la = operand(rng, O.F32, 256, 256, "c")
+    # f32: small products stay on the CUDA cores, large ones take the split-TF32 tensor path
+    a, la = operand(rng, O.F32, 128, 128, "c")
     _, path = gpu_matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)
     assert path == SIMT
+    a, la = operand(rng, O.F32, 512, 512, "c")
+    _, path = gpu_matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)
+    assert path == TENSOR
 
 
 def test_aliased_inputs_and_k_zero():
