@@ -25,6 +25,7 @@ SIGNATURES = {
     "hodu_b200_swiglu": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
     "hodu_b200_matmul_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
+    "hodu_b200_dot_f32_static": (_i, [_i, _vp, _vp, _vp, _vp, _szp, _sz]),
     "hodu_b200_strerror": (C.c_char_p, [_i]),
     "hodu_b200_last_error_message": (C.c_char_p, []),
     "hodu_b200_last_status": (_i, [_i, C.POINTER(C.c_uint32)]),

@@ -14,6 +14,8 @@
 // Step 2: the tcgen05 kernel (gemm_tc.cu, kind::tf32) multiplies A' [M,3K] by B' [3K,N].
 // The scratch comes from the stream-ordered allocator on the caller's stream, so concurrent
 // calls on different streams never share it.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace hodu_b200 {
@@ -185,3 +187,86 @@ int launch_gemm_f32(const Problem& pb, DeviceState* st, cudaStream_t stream, con
 }
 
 }  // namespace hodu_b200
+
+// ---------------------------------------------------------------------------------------------
+// hodu_b200_dot_f32_static: the same f32 product for callers that must not allocate device
+// memory at call time (see include/hodu_b200.h).  The split operands live in the fixed array
+// below instead of stream-ordered scratch.  Everything else -- split pass, tcgen05 kernel -- is
+// the code above, unchanged.
+// ---------------------------------------------------------------------------------------------
+namespace hodu_b200 {
+namespace {
+
+constexpr size_t kStaticScratchBytes = HODU_B200_STATIC_SCRATCH_BYTES;
+
+// Held by every GPU that loads the library, from load until exit.  In host code these names
+// are only handles for cudaGetSymbolAddress; kernels get the address that call returns.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ uint32_t g_static_status;
+
+struct StaticSetup {
+  bool done = false;
+  void* scratch = nullptr;     // device address of g_static_scratch on this device
+  uint32_t* status = nullptr;  // device address of g_static_status on this device
+  int sm_count = 0, cc_major = 0;
+};
+StaticSetup g_static_setup[kMaxDevices];
+std::mutex g_static_mu;
+
+// Once per device, with that device current: resolve the device addresses of the two symbols.
+int static_setup(int device, StaticSetup** out) {
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticSetup* s = &g_static_setup[device];
+  if (!s->done) {
+    HODU_CUDA_TRY(cudaGetSymbolAddress(&s->scratch, g_static_scratch), HODU_B200_ERR_MEMORY);
+    HODU_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&s->status), g_static_status), HODU_B200_ERR_MEMORY);
+    HODU_CUDA_TRY(cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, device), HODU_B200_ERR_LAUNCH);
+    HODU_CUDA_TRY(cudaDeviceGetAttribute(&s->cc_major, cudaDevAttrComputeCapabilityMajor, device), HODU_B200_ERR_LAUNCH);
+    if (s->scratch == nullptr || s->status == nullptr)
+      return fail(HODU_B200_ERR_MEMORY, "cudaGetSymbolAddress returned a null device address");
+    s->done = true;
+  }
+  *out = s;
+  return 0;
+}
+
+}  // namespace
+}  // namespace hodu_b200
+
+extern "C" int hodu_b200_dot_f32_static(int device, void* stream, const void* lhs, const void* rhs,
+                                        void* out, const size_t* metadata, size_t metadata_len) {
+  using namespace hodu_b200;
+  Problem pb;
+  int r = parse_dot(metadata, metadata_len, &pb);
+  if (r) return r;
+  if (pb.M == 0 || pb.N == 0) return 0;
+  if (!out) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
+  if (device < 0 || device >= kMaxDevices)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "device %d out of range 0..%d", device, kMaxDevices - 1);
+  pb.in_dtype = HODU_DTYPE_F32; pb.out_dtype = HODU_DTYPE_F32;
+  pb.a.ptr = lhs; pb.b.ptr = rhs; pb.out = out;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+  if (pb.K == 0) {  // an empty sum is zero; a memset allocates nothing
+    HODU_CUDA_TRY(cudaMemsetAsync(out, 0, static_cast<size_t>(pb.M) * pb.N * sizeof(float), s), HODU_B200_ERR_MEMORY);
+    return 0;
+  }
+  if (!lhs || !rhs) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
+  const size_t need = gemm_f32_scratch_bytes(pb);
+  if (need == 0 || need > kStaticScratchBytes)
+    return fail(HODU_B200_ERR_INVALID_INPUT,
+                "dot_f32_static: this product needs %zu bytes of scratch, the fixed array holds %zu "
+                "(12*(M+N)*K bytes must fit); use hodu_b200_dot for larger products",
+                need, kStaticScratchBytes);
+  StaticSetup* ss = nullptr;
+  r = static_setup(device, &ss);
+  if (r) return r;
+  DeviceState st;  // a local view: nothing of the library's allocated per-device state is touched
+  st.ready = true; st.sm_count = ss->sm_count; st.cc_major = ss->cc_major; st.status = ss->status;
+  const char* why = "";
+  r = launch_gemm_f32_split(pb, &st, s, ss->scratch, kStaticScratchBytes, &why);
+  if (r == 1) return fail(HODU_B200_ERR_INVALID_INPUT, "dot_f32_static refused: %s", why);
+  if (r == 0) set_last_path(HODU_B200_PATH_TENSOR);
+  return r;
+}

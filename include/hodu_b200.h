@@ -194,6 +194,41 @@ int hodu_b200_dot_host(int device, uint8_t in_dtype, uint8_t out_dtype,
                        const size_t* metadata, size_t metadata_len,
                        float scale_lhs, float scale_rhs);
 
+/*
+ * 2-D f32 product that allocates NOTHING.  It has no counterpart in the reference (whose
+ * wrappers allocate on every call: the metadata copy in
+ * crates/hodu_cuda_kernels/src/kernels/ops_matrix.rs:572-582).
+ *
+ * Who needs it: code that may not reach the device allocator while it runs -- a real-time
+ * loop that must not take the allocator's lock or risk the implicit device synchronisation an
+ * allocation can bring, a process that runs inside a fixed memory reservation where a late
+ * allocation can fail, a plug-in called from a host that forbids allocation in its compute
+ * callbacks.  hodu_b200_dot computes
+ * an f32 product through split TF32 operands that it keeps in scratch memory taken from the
+ * stream-ordered allocator; this entry point runs the same kernels with that scratch in a
+ * fixed array compiled into the library instead.  It calls no cudaMalloc / cudaFree /
+ * cudaMallocAsync and does not touch the library's per-device state (hodu_b200_init is not
+ * needed and is not called).
+ *
+ *  - metadata: the dot wire format, as hodu_b200_dot; any strides and offsets.
+ *  - Limit: the split operands take 12*(M+N)*K bytes (rows padded to 16 bytes) and must fit
+ *    HODU_B200_STATIC_SCRATCH_BYTES; larger products are rejected with
+ *    HODU_B200_ERR_INVALID_INPUT and a message naming both sizes.  Every GPU that loads the
+ *    library holds the array (that many bytes) from load to exit, used or not.
+ *  - The first call on a device resolves the array's device address (cudaGetSymbolAddress,
+ *    with that device current) and sets kernel attributes.  Make that first call before any
+ *    stream capture begins.
+ *  - All calls on a device share the one array, and it keeps the previous call's contents.
+ *    Nothing in it has to start at zero: each call overwrites every element it later reads.
+ *    Two calls whose kernels can overlap on the GPU (different streams without an ordering
+ *    between them) race on it; order them.
+ *  - A bounded wait that runs out is recorded in a device word private to this entry point,
+ *    not in the word hodu_b200_last_status reads.
+ */
+#define HODU_B200_STATIC_SCRATCH_BYTES (32u << 20)
+int hodu_b200_dot_f32_static(int device, void* stream, const void* lhs, const void* rhs, void* out,
+                             const size_t* metadata, size_t metadata_len);
+
 /* Text for an error code (static storage).  Mirrors `Display for CudaKernelError`
  * (crates/hodu_cuda_kernels/src/error.rs:20-32). */
 const char* hodu_b200_strerror(int code);
