@@ -43,7 +43,7 @@ WORKLOADS = {
 }
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"c2": None, "c3": None, "c4": None, "c5": None, "c1": None}
+NCU_TRAFFIC_BYTES = {"c2": 378.5e6, "c3": None, "c4": None, "c5": None, "c1": None}  # profiles/gemm_tc_pair_bf16_config2.md
 NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0}
 
 
