@@ -22,6 +22,7 @@ SIGNATURES = {
     "hodu_b200_matmul_ex": (_i, [_i, _vp, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f, _u32]),
     "hodu_b200_dot_ex": (_i, [_i, _vp, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f, _u32]),
     "hodu_b200_cast": (_i, [_i, _vp, _u8, _u8, _vp, _vp, _szp, _sz]),
+    "hodu_b200_contiguous": (_i, [_i, _vp, _u8, _vp, _vp, _szp, _sz]),
     "hodu_b200_swiglu": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
     "hodu_b200_matmul_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),

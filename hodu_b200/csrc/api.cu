@@ -25,6 +25,7 @@ DeviceState g_state[kMaxDevices];
 // Tensor-core path only above this much work; below it one CUDA-core CTA wave
 // finishes sooner than the TMA/TMEM pipeline fills.
 constexpr long long kTensorMinWork = 1ll << 21;     // M*N*K*batches
+constexpr long long kTensorMinWorkRelayout = 1ll << 24;  // an operand copy precedes the product
 constexpr long long kTensorMinWorkF32 = 1ll << 24;  // f32 pays two operand-split launches first
 }  // namespace
 
@@ -210,6 +211,13 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream) {
                                                 : launch_gemm_tc(pb, st, stream, &why);
     if (r == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
     if (r < 0) return r;
+    // A layout TMA cannot take: with enough work to pay for it, copy the operand(s) first.
+    if (work >= kTensorMinWorkRelayout || forced_tc) {
+      const char* why2 = "";
+      const int r2 = launch_gemm_tc_relayout(pb, st, stream, &why2);
+      if (r2 == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
+      if (r2 < 0) return r2;
+    }
     if (forced_tc) return fail(HODU_B200_ERR_INVALID_INPUT, "tensor-core path refused: %s", why);
   }
   set_last_path(HODU_B200_PATH_SIMT);
@@ -295,6 +303,12 @@ int hodu_b200_dot_ex(int device, void* stream, uint8_t in_dtype, uint8_t out_dty
 int hodu_b200_cast(int device, void* stream, uint8_t src, uint8_t dst, const void* in, void* out,
                    const size_t* md, size_t len) {
   return launch_cast(src, dst, in, out, md, len, device, static_cast<cudaStream_t>(stream));
+}
+
+int hodu_b200_contiguous(int device, void* stream, uint8_t dtype, const void* in, void* out,
+                         const size_t* md, size_t len) {
+  if (dtype_size(dtype) == 0) return fail(HODU_B200_ERR_INVALID_KERNEL, "contiguous: unknown dtype %d", dtype);
+  return launch_cast(dtype, dtype, in, out, md, len, device, static_cast<cudaStream_t>(stream));
 }
 
 int hodu_b200_swiglu(int device, void* stream, uint8_t dtype, const void* x, const void* w_gate,

@@ -30,6 +30,18 @@ template <> struct Conv<__nv_bfloat16, float> { static __device__ float f(__nv_b
 template <> struct Conv<__half, float> { static __device__ float f(__half x) { return __half2float(x); } };
 template <> struct Conv<__nv_fp8_e4m3, float> { static __device__ float f(__nv_fp8_e4m3 x) { return static_cast<float>(x); } };
 template <> struct Conv<int8_t, int32_t> { static __device__ int32_t f(int8_t x) { return x; } };
+// The remaining pairs hodu_core wires for CUDA (be_cuda/storage.rs:652-673), with the
+// reference's conversions: (double)x, (float)x, (int32_t)x (toward zero), (float)i
+// (ops_cast.cu:119,126,134,239).
+template <> struct Conv<float, double> { static __device__ double f(float x) { return static_cast<double>(x); } };
+template <> struct Conv<double, float> { static __device__ float f(double x) { return static_cast<float>(x); } };
+template <> struct Conv<float, int32_t> { static __device__ int32_t f(float x) { return static_cast<int32_t>(x); } };
+template <> struct Conv<int32_t, float> { static __device__ float f(int32_t x) { return static_cast<float>(x); } };
+// Same-type "conversion": the strided -> contiguous copy (`contiguous`), by element width.
+template <> struct Conv<uint8_t, uint8_t> { static __device__ uint8_t f(uint8_t x) { return x; } };
+template <> struct Conv<uint16_t, uint16_t> { static __device__ uint16_t f(uint16_t x) { return x; } };
+template <> struct Conv<uint32_t, uint32_t> { static __device__ uint32_t f(uint32_t x) { return x; } };
+template <> struct Conv<uint64_t, uint64_t> { static __device__ uint64_t f(uint64_t x) { return x; } };
 
 template <typename T, int N> struct alignas(sizeof(T) * N) Pack { T v[N]; };
 
@@ -153,7 +165,10 @@ int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, s
   const uint8_t* base = static_cast<const uint8_t*>(in) + offset * dtype_size(src);
   const bool known = (src == HODU_DTYPE_F32 && (dst == HODU_DTYPE_BF16 || dst == HODU_DTYPE_F16 || dst == HODU_DTYPE_F8E4M3)) ||
                      (dst == HODU_DTYPE_F32 && (src == HODU_DTYPE_BF16 || src == HODU_DTYPE_F16 || src == HODU_DTYPE_F8E4M3)) ||
-                     (src == HODU_DTYPE_I8 && dst == HODU_DTYPE_I32);
+                     (src == HODU_DTYPE_I8 && dst == HODU_DTYPE_I32) ||
+                     (src == HODU_DTYPE_F32 && (dst == HODU_DTYPE_F64 || dst == HODU_DTYPE_I32)) ||
+                     (dst == HODU_DTYPE_F32 && (src == HODU_DTYPE_F64 || src == HODU_DTYPE_I32)) ||
+                     (src == dst && dtype_size(src) > 0);
   if (!known) return fail(HODU_B200_ERR_INVALID_KERNEL, "cast: unsupported pair %s -> %s", dtype_name(src), dtype_name(dst));
   // Arguments are valid: only now is the device touched.
   DeviceState* st = device_state(device);
@@ -170,7 +185,20 @@ int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, s
   HODU_CAST(HODU_DTYPE_F16, HODU_DTYPE_F32, __half, float);
   HODU_CAST(HODU_DTYPE_F8E4M3, HODU_DTYPE_F32, __nv_fp8_e4m3, float);
   HODU_CAST(HODU_DTYPE_I8, HODU_DTYPE_I32, int8_t, int32_t);
+  HODU_CAST(HODU_DTYPE_F32, HODU_DTYPE_F64, float, double);
+  HODU_CAST(HODU_DTYPE_F64, HODU_DTYPE_F32, double, float);
+  HODU_CAST(HODU_DTYPE_F32, HODU_DTYPE_I32, float, int32_t);
+  HODU_CAST(HODU_DTYPE_I32, HODU_DTYPE_F32, int32_t, float);
 #undef HODU_CAST
+  if (src == dst) {
+    switch (dtype_size(src)) {
+      case 1: return run_cast<uint8_t, uint8_t>(base, out, n, contiguous, m, st, stream);
+      case 2: return run_cast<uint16_t, uint16_t>(base, out, n, contiguous, m, st, stream);
+      case 4: return run_cast<uint32_t, uint32_t>(base, out, n, contiguous, m, st, stream);
+      case 8: return run_cast<uint64_t, uint64_t>(base, out, n, contiguous, m, st, stream);
+      default: break;
+    }
+  }
   return fail(HODU_B200_ERR_INVALID_KERNEL, "cast: unsupported pair %s -> %s", dtype_name(src), dtype_name(dst));
 }
 

@@ -89,6 +89,10 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream);
 // tcgen05 kernel. Returns 1 if the layout cannot be described to TMA (nothing
 // launched, `why` says which rule failed), 0 when launched, <0 on error.
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// Layout front door (relayout.cu): copies the operands TMA cannot describe into scratch as
+// K-contiguous matrices, then runs the tensor-core kernel.  1 = nothing to fix / not applicable.
+bool tc_operand_describable(const Problem& pb, const Operand& op, bool is_lhs, int esize);
+int launch_gemm_tc_relayout(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
 // f32 on the tensor cores through split TF32 operands held in scratch memory (gemm_f32.cu).
 // Return convention as launch_gemm_tc.  `launch_gemm_f32` takes the scratch from the
 // stream-ordered allocator; `launch_gemm_f32_split` uses the scratch it is given.

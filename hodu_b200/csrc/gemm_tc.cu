@@ -793,6 +793,17 @@ int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t lim
   return 0;
 }
 
+// Whether TMA can describe `op` as it lies in memory (the per-operand rules of build_operand_map).
+bool tc_operand_describable(const Problem& pb, const Operand& op, bool is_lhs, int esize) {
+  const int64_t rows = is_lhs ? pb.M : pb.K, cols = is_lhs ? pb.K : pb.N;
+  const uintptr_t base = reinterpret_cast<uintptr_t>(op.ptr) + static_cast<uintptr_t>(op.offset) * esize;
+  if (base % 16 != 0 || rows > 0xFFFFFFFFll || cols > 0xFFFFFFFFll) return false;
+  if (classify_operand(op, esize, rows, cols, is_lhs) < 0) return false;
+  for (int d = 0; d < pb.batch_ndim; ++d)
+    if (pb.batch_shape[d] > 1 && op.bstride[d] != 0 && !pitch_ok(op.bstride[d], esize)) return false;
+  return true;
+}
+
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
   static const char* none = "";
   *why = none;

@@ -39,6 +39,7 @@ class _Family:
         return Kernel(f"hodu_cuda_{self._op}_{dtype_upper.lower()}")
 
 
+contiguous = _Family("contiguous")
 matmul = _Family("matmul")
 dot = _Family("dot")
 cast = _Family("cast")
@@ -77,6 +78,14 @@ def call_ops_cast(kernel: Kernel, device: int, input: int, output: int,
     src, dst = _parse(kernel, "cast")
     md = metadata_array(metadata)
     check(_lib.lib().hodu_b200_cast(device, stream, int(src), int(dst), input, output, md, len(metadata)))
+
+
+def call_ops_contiguous(kernel: Kernel, device: int, input: int, output: int,
+                        metadata: Sequence[int], stream: int = 0) -> None:
+    """`call_ops_contiguous` (hodu_cuda_contiguous_{dtype}): strided -> contiguous copy."""
+    dt = _parse(kernel, "contiguous")
+    md = metadata_array(metadata)
+    check(_lib.lib().hodu_b200_contiguous(device, stream, int(dt), input, output, md, len(metadata)))
 
 
 # ---- extensions with no counterpart in the reference crate -------------------------------

@@ -149,6 +149,17 @@ class Tensor:
                                        self.storage.data_ptr(), other.storage.data_ptr(), out.data_ptr(),
                                        md, scale_lhs, scale_rhs, s, is_dot=is_dot)
 
+    def contiguous(self) -> "Tensor":
+        """`CudaStorage::contiguous` (be_cuda/storage.rs:681-709): a dense copy of the view;
+        the tensor itself when it already is contiguous."""
+        if self.layout.is_contiguous() and self.layout.offset == 0 and self.storage.numel() == self.layout.size():
+            return self
+        out = torch.empty(self.layout.size(), dtype=self.storage.dtype, device=self.storage.device)
+        k = getattr(kernels.contiguous, str(self.dtype).upper())
+        kernels.call_ops_contiguous(k, self.device_id, self.storage.data_ptr(), out.data_ptr(),
+                                    cast_metadata(self.layout), _stream(self.storage.device))
+        return Tensor(out, Layout.from_shape(self.layout.shape))
+
     # ---- casts ----------------------------------------------------------------------------
     def to_dtype(self, dtype: DType) -> "Tensor":
         """`Tensor::to_dtype` -> `CudaStorage::to_dtype` -> `call_ops_cast`; output is contiguous."""
@@ -160,6 +171,21 @@ class Tensor:
         kernels.call_ops_cast(k, self.device_id, self.storage.data_ptr(), out.data_ptr(),
                               cast_metadata(self.layout), _stream(self.storage.device))
         return Tensor(out, Layout.from_shape(self.layout.shape))
+
+
+def matmul_vjp(a: Tensor, b: Tensor, grad_output: Tensor):
+    """Vector-Jacobian products of `a.matmul(b)` as the reference computes them
+    (crates/hodu_core/src/tensor/gradient/vjp_matrix.rs:17-66): dA = grad @ B^T and
+    dB = A^T @ grad, both through transposed VIEWS (no copies), i.e. a K-contiguous rhs and an
+    M-contiguous lhs for the kernels.  Operands whose batch dims were broadcast would need the
+    reference's `sum_to_shape` reduction afterwards, which is not on this path: rejected."""
+    if len(a.shape) < 2 or len(b.shape) < 2:
+        raise HoduError("matmul_vjp takes operands of rank >= 2")
+    grad_a = grad_output.matmul(b.transpose(-2, -1))
+    grad_b = a.transpose(-2, -1).matmul(grad_output)
+    if grad_a.shape != a.shape or grad_b.shape != b.shape:
+        raise HoduError("broadcast batch dims need sum_to_shape, which is outside the matmul path")
+    return grad_a, grad_b
 
 
 def _validate_pair(a: Tensor, b: Tensor) -> None:

@@ -150,13 +150,22 @@ int hodu_b200_dot_ex(int device, void* stream, uint8_t in_dtype, uint8_t out_dty
  * Element-wise dtype conversion.  Replaces `call_ops_cast`
  * (crates/hodu_cuda_kernels/src/kernels/ops_cast.rs:27-64) and
  * `hodu_cuda_cast_{src}_to_{dst}` (crates/hodu_cuda_kernels/kernels/ops_cast.cu:7-30)
- * for f32 <-> bf16 | f16 | f8e4m3 and i8 -> i32.
+ * for f32 <-> bf16 | f16 | f8e4m3, i8 -> i32, and the pairs hodu_core wires for CUDA today:
+ * f32 <-> f64, f32 <-> i32 (crates/hodu_core/src/be_cuda/storage.rs:652-673).
  * metadata = [num_els, ndim, shape.., strides.., offset]
  * (crates/hodu_core/src/op_metadatas.rs:1615-1640).
  */
 int hodu_b200_cast(int device, void* stream, uint8_t src_dtype, uint8_t dst_dtype,
                    const void* in, void* out,
                    const size_t* metadata, size_t metadata_len);
+
+/*
+ * Strided -> contiguous copy of any dtype.  Replaces `call_ops_contiguous` and
+ * `hodu_cuda_contiguous_{dtype}` (crates/hodu_cuda_kernels/kernels/ops_memory.cu:6-27; call
+ * site crates/hodu_core/src/be_cuda/storage.rs:681-709).  metadata as for hodu_b200_cast.
+ */
+int hodu_b200_contiguous(int device, void* stream, uint8_t dtype, const void* in, void* out,
+                         const size_t* metadata, size_t metadata_len);
 
 /*
  * Fused gate/up half of a SwiGLU MLP:  out[M,N] = silu(x . w_gate) * (x . w_up).

@@ -134,9 +134,7 @@ def test_batched_broadcast(lshape, rshape, in_dt, out_dt, as_views):
     out_l = Layout.from_shape((*batch, lshape[-2], rshape[-1]))
     md = matmul_metadata(la, lb, out_l)
     want = O.matmul(a, b, md, in_dt, out_dt)
-    esize = np.dtype(O.NP_STORAGE[in_dt]).itemsize
-    tma_ok = all((d * esize) % 16 == 0 for d in (lshape[-1], rshape[-1]))  # row pitches TMA can take
-    paths = [SIMT, TENSOR] if (tma_ok or in_dt == O.F32) else [SIMT]  # the f32 path re-lays its operands
+    paths = [SIMT, TENSOR]  # pitches TMA cannot take are re-laid into scratch on the tensor path
     for path in paths:
         got, taken = gpu_matmul(a, b, md, in_dt, out_dt, path=path)
         assert taken == path
@@ -169,6 +167,30 @@ def test_f32_on_tensor_cores_keeps_f32_accuracy(a_c, b_c):
     assert O.rel_err(got, O.matmul(a, b, md, O.F32, is_dot=True)) <= 1e-5
 
 
+@pytest.mark.parametrize("in_dt,out_dt", [(O.BF16, O.BF16), (O.F16, O.F32), (O.F8E4M3, O.BF16), (O.I8, O.I32)])
+def test_layout_front_door_relays_what_tma_cannot_take(in_dt, out_dt):
+    """Odd pitches, odd element offsets and doubly-strided operands on the tensor path: the
+    operand is copied into scratch as a dense K-contiguous matrix first."""
+    rng = np.random.default_rng(41 + in_dt)
+    cases = [
+        # (M, K, N, lhs layout maker, rhs layout maker)
+        (200, 301, 136, lambda m, k: Layout((m, k), (k + 3, 1), 5), lambda k, n: Layout((k, n), (n + 1, 1), 7)),
+        (136, 264, 200, lambda m, k: Layout((m, k), (1, m + 5), 1), lambda k, n: Layout((k, n), (1, k + 9), 3)),   # transposed, odd pitch
+        (130, 96, 70, lambda m, k: Layout((m, k), (2 * k, 2), 0), lambda k, n: Layout((k, n), (3 * n, 3), 0)),     # no contiguous index
+    ]
+    for m, k, n, mk_a, mk_b in cases:
+        la, lb = mk_a(m, k), mk_b(k, n)
+        size_a = la.offset + sum((s - 1) * st for s, st in zip(la.shape, la.strides)) + 1
+        size_b = lb.offset + sum((s - 1) * st for s, st in zip(lb.shape, lb.strides)) + 1
+        a, b = rand_storage(rng, in_dt, (size_a,)), rand_storage(rng, in_dt, (size_b,))
+        md = dot_metadata(la, lb)
+        want = O.matmul(a, b, md, in_dt, out_dt, is_dot=True)
+        for path in (TENSOR, _lib.PATH_TENSOR_2CTA):
+            got, taken = gpu_matmul(a, b, md, in_dt, out_dt, is_dot=True, path=path)
+            assert taken == TENSOR
+            check_close(got, want, out_dt, TOL.get(in_dt, 0))
+
+
 def test_offsets_on_tensor_path():
     """Views into a larger buffer: 16-byte-aligned element offsets and padded pitches."""
     rng = np.random.default_rng(3)
@@ -187,15 +209,26 @@ def test_auto_path_selection_and_refusal():
     b, lb = operand(rng, O.BF16, 256, 256, "c")
     _, path = gpu_matmul(a, b, dot_metadata(la, lb), O.BF16, is_dot=True)
     assert path == TENSOR
-    # K = 37: row pitch of 74 bytes cannot be a TMA stride -> CUDA-core kernel, same answer bar
+    # K = 297: a row pitch of 594 bytes cannot be a TMA stride.  Large enough to pay for a copy:
+    # the operands are re-laid into scratch and the tensor cores still run
     a, la = operand(rng, O.BF16, 256, 37 * 8 + 1, "c")
-    b, lb = operand(rng, O.BF16, 37 * 8 + 1, 256, "c")
+    b, lb = operand(rng, O.BF16, 37 * 8 + 1, 256, "r")
+    md = dot_metadata(la, lb)
+    got, path = gpu_matmul(a, b, md, O.BF16, is_dot=True)
+    assert path == TENSOR
+    check_close(got, O.matmul(a, b, md, O.BF16, is_dot=True), O.BF16, 1e-2)
+    # the same kind of layout, small: the generic CUDA-core kernel, same answer bar
+    a, la = operand(rng, O.BF16, 64, 37, "c")
+    b, lb = operand(rng, O.BF16, 37, 64, "c")
     md = dot_metadata(la, lb)
     got, path = gpu_matmul(a, b, md, O.BF16, is_dot=True)
     assert path == SIMT
     check_close(got, O.matmul(a, b, md, O.BF16, is_dot=True), O.BF16, 1e-2)
+    # a dtype with no tensor-core kernel is refused when the tensor path is forced, never re-routed
+    ai = rand_storage(rng, O.I32, (64, 64))
     with pytest.raises(CudaKernelError) as e:
-        gpu_matmul(a, b, md, O.BF16, is_dot=True, path=TENSOR)
+        gpu_matmul(ai, ai, dot_metadata(Layout.from_shape((64, 64)), Layout.from_shape((64, 64))), O.I32,
+                   is_dot=True, path=TENSOR)
     assert e.value.kind == "invalid input" and "tensor-core path refused" in str(e.value)
     # f32: small products stay on the CUDA cores, large ones take the split-TF32 tensor path
     a, la = operand(rng, O.F32, 128, 128, "c")
