@@ -37,7 +37,7 @@ SIGNATURES = {
     "hodu_b200_version": (_i, []),
 }
 
-PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_TENSOR_1CTA, PATH_TENSOR_2CTA = 0, 1, 2, 3, 4
+PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_TENSOR_1CTA, PATH_TENSOR_2CTA, PATH_TENSOR_2CTA_512 = 0, 1, 2, 3, 4, 5
 SWIGLU_ROUND_EACH_OP, SWIGLU_ROUND_ONCE = 0, 1
 
 

@@ -49,7 +49,7 @@ int forced_path() {
   // HODU_B200_FORCE_PATH=<n> presets the selector (same values as hodu_b200_force_path).
   static const bool env_read = [] {
     const char* e = getenv("HODU_B200_FORCE_PATH");
-    if (e && e[0] >= '0' && e[0] <= '4' && e[1] == 0) g_forced_path.store(e[0] - '0');
+    if (e && e[0] >= '0' && e[0] <= '5' && e[1] == 0) g_forced_path.store(e[0] - '0');
     return true;
   }();
   (void)env_read;
@@ -201,8 +201,7 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   if (pb.K == 0) { set_last_path(HODU_B200_PATH_AUTO); return zero_output(pb, stream); }
   const int forced = forced_path();
   const long long work = static_cast<long long>(pb.M) * pb.N * pb.K * pb.batches;
-  const bool forced_tc = forced == HODU_B200_PATH_TENSOR || forced == HODU_B200_PATH_TENSOR_1CTA ||
-                         forced == HODU_B200_PATH_TENSOR_2CTA;
+  const bool forced_tc = forced >= HODU_B200_PATH_TENSOR && forced <= HODU_B200_PATH_TENSOR_2CTA_512;
   const long long min_work = pb.in_dtype == HODU_DTYPE_F32 ? kTensorMinWorkF32 : kTensorMinWork;
   const bool want_tc = forced_tc || (forced == HODU_B200_PATH_AUTO && work >= min_work);
   if (want_tc) {
@@ -377,7 +376,7 @@ int hodu_b200_debug_wait_timeout(int device, void* stream, uint32_t limit_ms) {
 }
 
 int hodu_b200_force_path(int path) {
-  if (path < HODU_B200_PATH_AUTO || path > HODU_B200_PATH_TENSOR_2CTA) return HODU_B200_ERR_INVALID_INPUT;
+  if (path < HODU_B200_PATH_AUTO || path > HODU_B200_PATH_TENSOR_2CTA_512) return HODU_B200_ERR_INVALID_INPUT;
   return g_forced_path.exchange(path);
 }
 int hodu_b200_last_path(void) { return g_last_path; }

@@ -38,17 +38,21 @@ using namespace ptx;
 namespace {
 
 constexpr int BM = 128;                 // rows of A one CTA stages == TMEM lanes
-constexpr int kThreads = 224;           // 7 warps, see the role table above
-constexpr int kStageA = BM * 128;       // bytes: 128 rows (or M elements) x 128 B of K
+constexpr int kHalfA = BM * 128;        // bytes: 128 rows (or M elements) x 128 B of K
+// 7 warps (see the role table above); with two M-halves per CTA a second group of four
+// epilogue warps (7..10) drains the second accumulator.
+constexpr int threads_for(int mh) { return 224 + 128 * (mh - 1); }
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, OUT_I8 = 5 };
 
-// Stage ring per CTA.  PAIR: each CTA of the pair stages 128 columns of B.
-template <int BN, bool PAIR> struct TileCfg {
+// Stage ring per CTA.  PAIR: each CTA of the pair stages 128 columns of B.  MH = M-halves
+// (128-row accumulators) per CTA: 1, or 2 for the 512 x 256 pair tile.
+template <int BN, bool PAIR, int MH> struct TileCfg {
+  static constexpr int kStageA = MH * kHalfA;
   static constexpr int kStageB = PAIR ? 128 * 128 : BN * 128;
-  static constexpr int kStages = PAIR ? 7 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
-  static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
+  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 7) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators: double buffer (MH 1) or the two halves (MH 2)
 };
 
 struct SmemTail {
@@ -243,15 +247,15 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* dst, const uint32_t (&v
 // expect-tx arrive, TMA issue) of one never delays the other.
 //   PAIR: both CTAs of the pair signal CTA 0's `full` barriers; only CTA 0's producers
 //   arrive on them (with the byte count of both CTAs), CTA 1's just issue their loads.
-template <int BN, bool SWIGLU, bool PAIR, bool IS_A>
+template <int BN, bool SWIGLU, bool PAIR, int MH, bool IS_A>
 __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLoad& o,
                                               const CUtensorMap* map0, const CUtensorMap* map1,
                                               SmemTail* tail, uint32_t smem_operand, uint32_t rank,
                                               uint32_t first_tile, uint32_t tile_step,
                                               uint32_t code) {
-  using Cfg = TileCfg<BN, PAIR>;
+  using Cfg = TileCfg<BN, PAIR, MH>;
   constexpr int kStages = Cfg::kStages;
-  constexpr uint32_t kStageBytes = IS_A ? kStageA : Cfg::kStageB;
+  constexpr uint32_t kStageBytes = IS_A ? Cfg::kStageA : Cfg::kStageB;
   constexpr uint32_t kOutCols = SWIGLU ? BN / 2 : BN;
   volatile uint32_t* abort_flag = &tail->abort_flag;
   const uint32_t my_bytes = o.boxes * o.box_bytes;
@@ -269,7 +273,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
     const int32_t c_b1 = static_cast<int32_t>(b1 * o.bmul[1]);
     const int32_t c_b0 = static_cast<int32_t>(b0 * o.bmul[0]);
     int32_t mn0;
-    if (IS_A) mn0 = static_cast<int32_t>(tc.mt * (PAIR ? 256u : 128u) + rank * 128u);
+    if (IS_A) mn0 = static_cast<int32_t>(tc.mt * (PAIR ? 256u * MH : 128u) + rank * 128u * MH);
     else if (PAIR) mn0 = static_cast<int32_t>(SWIGLU ? tc.nt * 128u : tc.nt * 256u + rank * 128u);
     else mn0 = static_cast<int32_t>(tc.nt * kOutCols);
     for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
@@ -323,17 +327,19 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
 //   CTA runs its own epilogue.  Loads are plain per-CTA TMA loads; CTA 0's commits signal
 //   `empty` / `tmem_full` in both CTAs.  With SWIGLU, CTA 0 stages the gate weights and CTA 1
 //   the up weights of the same 128 output columns.
-template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
+__global__ void __launch_bounds__(threads_for(MH), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const TcParams p) {
-  using Cfg = TileCfg<BN, PAIR>;
+  static_assert(MH == 1 || (PAIR && BN == 256), "two M-halves per CTA exist for the pair form only");
+  using Cfg = TileCfg<BN, PAIR, MH>;
   constexpr int kStages = Cfg::kStages;
+  constexpr int kStageA = Cfg::kStageA;
   constexpr int kStageB = Cfg::kStageB;
   constexpr int CG = PAIR ? 2 : 1;
   constexpr bool kIntAcc = (KIND == KIND_I8);
   constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
-  constexpr uint32_t kTileM = PAIR ? 256u : 128u;
+  constexpr uint32_t kTileM = PAIR ? 256u * MH : 128u;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -380,14 +386,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------ producer of A
     if (lane == 0)
-      producer_role<BN, SWIGLU, PAIR, true>(p, p.a, &map_a, &map_a, tail, smem_a, rank, first_tile,
+      producer_role<BN, SWIGLU, PAIR, MH, true>(p, p.a, &map_a, &map_a, tail, smem_a, rank, first_tile,
                                             tile_step, code_base | 1u);
     __syncwarp();
   } else if (warp == 6) {
     // ------------------------------------------------------------ producer of B
     if (lane == 0) {
       const CUtensorMap* m0 = (PAIR && SWIGLU && rank == 1) ? &map_b2 : &map_b;
-      producer_role<BN, SWIGLU, PAIR, false>(p, p.b, m0, &map_b2, tail, smem_b, rank, first_tile,
+      producer_role<BN, SWIGLU, PAIR, MH, false>(p, p.b, m0, &map_b2, tail, smem_b, rank, first_tile,
                                              tile_step, code_base | 5u);
     }
     __syncwarp();
@@ -400,23 +406,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #ifdef HODU_TC_PROFILE
       long long prof_full = 0;
 #endif
+      // Issuing an MMA waits until the one before it has started, so the only slack for the
+      // per-stage bookkeeping (commit, barrier wait, fence) is the last MMA of a stage.  With one
+      // accumulator per CTA the wait for the NEXT stage is probed before that last MMA is
+      // issued (measured +2 %; with two accumulators per CTA it measured -2 % and is left out).
+      bool next_ready = false;
       for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step, ++lt) {
-        const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
-        PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
-                               code_base | 2u));
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        // MH == 1: the two accumulators alternate between tiles (double buffer).
+        // MH == 2: one tile fills both, accumulator h holding M-half h.
+        const uint32_t acc0 = MH == 2 ? 0u : (lt & 1u);
+        const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
+        for (uint32_t kb = 0; ok && kb < p.k_blocks; ++kb) {
 #ifdef HODU_TC_PROFILE
           const long long tw = clock64();
 #endif
-          ok = wait_bounded(smem_u32(&tail->full[s]), ph, abort_flag, p.status, code_base | 3u);
+          if (!next_ready)
+            ok = wait_bounded(smem_u32(&tail->full[s]), ph, abort_flag, p.status, code_base | 3u);
 #ifdef HODU_TC_PROFILE
           prof_full += clock64() - tw;
 #endif
           if (!ok) break;
           tc_fence_after_sync();
+          const uint32_t ns = (s + 1 == kStages) ? 0u : s + 1u;
+          const uint32_t nph = (s + 1 == kStages) ? ph ^ 1u : ph;
 #ifdef HODU_TC_PROFILE
           if (p.out_vec_ok & 4u) {  // experiment: loads only, no MMAs
             mbar_arrive(smem_u32(&tail->empty[s]));
@@ -425,26 +437,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             continue;
           }
 #endif
-          const uint32_t a16 = (smem_a + s * kStageA) >> 4;
           const uint32_t b16 = (smem_b + s * kStageB) >> 4;
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {
-            const uint64_t adesc =
-                (static_cast<uint64_t>(p.a.desc_hi) << 32) |
-                static_cast<uint64_t>(((a16 + k * p.a.kstep16) & 0x3FFFu) | p.a.desc_lo);
-            const uint64_t bdesc =
-                (static_cast<uint64_t>(p.b.desc_hi) << 32) |
-                static_cast<uint64_t>(((b16 + k * p.b.kstep16) & 0x3FFFu) | p.b.desc_lo);
-            umma<KIND, CG>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0u ? 1u : 0u);
+          for (uint32_t h = 0; h < static_cast<uint32_t>(MH); ++h) {
+            const uint32_t acc = acc0 + h;
+            if (kb == 0) {  // first write of this accumulator: the epilogue must have drained it
+              PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
+                                     code_base | 2u));
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            const uint32_t a16 = (smem_a + s * kStageA + h * kHalfA) >> 4;
+            // Descriptor arithmetic sits between the MMA issues on purpose: an issue waits for
+            // the MMA before it to start, so these few instructions cost no tensor time, while
+            // the same work done ahead of the first MMA of a stage would.
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+              const uint64_t adesc =
+                  (static_cast<uint64_t>(p.a.desc_hi) << 32) |
+                  static_cast<uint64_t>(((a16 + k * p.a.kstep16) & 0x3FFFu) | p.a.desc_lo);
+              const uint64_t bdesc =
+                  (static_cast<uint64_t>(p.b.desc_hi) << 32) |
+                  static_cast<uint64_t>(((b16 + k * p.b.kstep16) & 0x3FFFu) | p.b.desc_lo);
+              if constexpr (MH == 1) {  // probe the next stage while the last MMA of this one is pending
+                if (k == 3u) next_ready = mbar_test_wait(smem_u32(&tail->full[ns]), nph);
+              }
+              umma<KIND, CG>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0u ? 1u : 0u);
+            }
+            if (kb + 1 == p.k_blocks) {  // this accumulator is complete once these MMAs retire
+              if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->tmem_full[acc]), 3);
+              else umma_commit_1cta(smem_u32(&tail->tmem_full[acc]));
+            }
           }
+          if (!ok) break;
           // frees the stage (in both CTAs of a pair) when these MMAs retire
           if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->empty[s]), 3);
           else umma_commit_1cta(smem_u32(&tail->empty[s]));
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
-        if (!ok) break;
-        if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->tmem_full[acc]), 3);
-        else umma_commit_1cta(smem_u32(&tail->tmem_full[acc]));
       }
       PROF_DUMP(1);
 #ifdef HODU_TC_PROFILE
@@ -458,21 +489,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
+    // ------------------------------------------------------------ epilogue (warps 2..5, and 7..10 when MH == 2)
+    const uint32_t q = warp & 3u;            // TMEM lane quadrant this warp may read
+    const uint32_t half = warp >= 7u ? 1u : 0u;  // MH == 2: which M-half (accumulator) this warp group drains
     const uint32_t osz = OutBytes<OUT>::value;
     const uint32_t tmem_empty0 =
         PAIR ? mapa_shared(smem_u32(&tail->tmem_empty[0]), 0u) : smem_u32(&tail->tmem_empty[0]);
     uint32_t lt = 0;
     for (uint32_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt) {
-      const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
+      const uint32_t acc = MH == 2 ? half : (lt & 1u);
+      const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
       bool ok = wait_bounded(smem_u32(&tail->tmem_full[acc]), acc_ph, abort_flag, p.status,
                              code_base | 4u);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after_sync();
       const TileCoord tc = decode_tile(p, t);
-      const uint32_t row = tc.mt * kTileM + rank * 128u + q * 32u + lane;
+      const uint32_t row = tc.mt * kTileM + rank * 128u * MH + half * 128u + q * 32u + lane;
       const uint32_t n0 = tc.nt * kOutCols;
       const bool row_ok = row < p.M;
       uint8_t* out_row = static_cast<uint8_t*>(p.out) +
@@ -722,15 +755,15 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   return nullptr;
 }
 
-template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR>
+template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
 int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
                 const TcParams& p, int device, int sm_count, cudaStream_t stream) {
-  using Cfg = TileCfg<BN, PAIR>;
-  constexpr size_t smem = Cfg::kStages * (kStageA + Cfg::kStageB) + sizeof(SmemTail) + 1024;
+  using Cfg = TileCfg<BN, PAIR, MH>;
+  constexpr size_t smem = Cfg::kStages * (Cfg::kStageA + Cfg::kStageB) + sizeof(SmemTail) + 1024;
   static int max_ctas[kMaxDevices] = {0};  // CTAs (1-CTA form) or CTA pairs that can be resident
-  auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU, PAIR>;
+  auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU, PAIR, MH>;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(threads_for(MH), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -755,7 +788,7 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   cfg.gridDim = dim3(PAIR ? 2 * units : units, 1, 1);
   if (debug_enabled())
     fprintf(stderr, "[hodu_b200] gemm_tc %s: %u tiles of %dx%d, grid %u, %zu B smem, A %s x%u, B %s x%u%s\n",
-            PAIR ? "pair" : "1-CTA", p.num_tiles, PAIR ? 256 : 128, SWIGLU ? BN / 2 : BN, cfg.gridDim.x, smem,
+            PAIR ? "pair" : "1-CTA", p.num_tiles, PAIR ? 256 * MH : 128, SWIGLU ? BN / 2 : BN, cfg.gridDim.x, smem,
             p.a.mn_major ? "M-major" : "K-major", p.a.boxes, p.b.mn_major ? "N-major" : "K-major", p.b.boxes,
             p.b.slab_dim ? " (slab dim)" : "");
   HODU_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, mb2, p), HODU_B200_ERR_LAUNCH);
@@ -764,16 +797,17 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
 }
 
 template <int KIND, int OUT, bool SWIGLU>
-int launch_shape(int bn, bool pair, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+int launch_shape(int bn, int pair /* 0: 1-CTA, 1: 256x256 pair, 2: 512x256 pair */, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
                  const TcParams& p, int device, int sm_count, cudaStream_t stream) {
-  if (pair) return launch_inst<KIND, 256, OUT, SWIGLU, true>(ma, mb, mb2, p, device, sm_count, stream);
+  if (pair == 2) return launch_inst<KIND, 256, OUT, SWIGLU, true, 2>(ma, mb, mb2, p, device, sm_count, stream);
+  if (pair == 1) return launch_inst<KIND, 256, OUT, SWIGLU, true, 1>(ma, mb, mb2, p, device, sm_count, stream);
   if constexpr (SWIGLU) {
-    return launch_inst<KIND, 256, OUT, true, false>(ma, mb, mb2, p, device, sm_count, stream);
+    return launch_inst<KIND, 256, OUT, true, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
   } else {
     switch (bn) {
-      case 256: return launch_inst<KIND, 256, OUT, false, false>(ma, mb, mb2, p, device, sm_count, stream);
-      case 128: return launch_inst<KIND, 128, OUT, false, false>(ma, mb, mb2, p, device, sm_count, stream);
-      default: return launch_inst<KIND, 64, OUT, false, false>(ma, mb, mb2, p, device, sm_count, stream);
+      case 256: return launch_inst<KIND, 256, OUT, false, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
+      case 128: return launch_inst<KIND, 128, OUT, false, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
+      default: return launch_inst<KIND, 64, OUT, false, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
     }
   }
 }
@@ -827,26 +861,49 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   const int b_cls = classify_operand(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false);
   if (b_cls < 0) { *why = "rhs: neither matrix index is contiguous with a 16-byte-multiple pitch"; return 1; }
 
-  // Tile shape.  A CTA pair per 256 x 256 tile once there are enough such tiles to occupy the
-  // pairs; otherwise one CTA per 128 x BN tile with the widest BN that still gives every SM a
-  // tile (never more than twice as wide as N).  An 8-bit N-contiguous rhs needs BN >= 128:
-  // one 128-byte swizzle row holds 128 of its elements.
+  // Tile shape: the candidate with the least estimated time = waves x cycles per tile.
+  //   form 2: CTA pair, 512 x 256 tile, two 128-row accumulators per CTA (all of TMEM: the
+  //           epilogue of a tile is not hidden behind the next tile's main loop)
+  //   form 1: CTA pair, 256 x 256 tile, double-buffered accumulator
+  //   form 0: one CTA, 128 x BN tile; an 8-bit N-contiguous rhs needs BN >= 128 (one 128-byte
+  //           swizzle row holds 128 of its elements)
+  // Cycles per k-block = max(MMA cycles, operand bytes one SM takes in / ~50 B per cycle): the
+  // measured tensor-pipe utilisations (512x256: 0.9, 256x256: 0.78, 128x256: 0.53) follow the
+  // bytes per MMA cycle each form needs (48, 64, 96 B/clk), not DRAM or L2 bandwidth.
   const int forced = forced_path();
-  const int out_cols_pair = pb.swiglu ? 128 : 256;
-  const int64_t pair_tiles = ((pb.M + 255) / 256) * ((pb.N + out_cols_pair - 1) / out_cols_pair) * pb.batches;
-  bool use_pair = pb.M > 128 && (pb.swiglu || pb.N > 128) && pair_tiles * 2 >= st->sm_count / 2;
-  if (forced == HODU_B200_PATH_TENSOR_1CTA) use_pair = false;
-  if (forced == HODU_B200_PATH_TENSOR_2CTA) use_pair = true;
-  const int64_t tiles_m = use_pair ? (pb.M + 255) / 256 : (pb.M + BM - 1) / BM;
-  int bn = 256;
-  if (!pb.swiglu && !use_pair) {
-    const int min_bn = (b_cls == 1 && esize == 1) ? 128 : 64;
-    for (int c = 256; c >= min_bn; c >>= 1) {
-      if (c > min_bn && pb.N <= c / 2) continue;
-      bn = c;
-      if (tiles_m * ((pb.N + c - 1) / c) * pb.batches >= st->sm_count) break;
+  const int units_pair = st->sm_count / 2 > 0 ? st->sm_count / 2 : 1;
+  const double k_blocks_d = static_cast<double>((pb.K + (128 / esize) - 1) / (128 / esize));
+  int form = 0, bn = 256;
+  {
+    double best = 1e300;
+    auto consider = [&](int f, int c) {
+      const int64_t tm = f == 2 ? 512 : (f == 1 ? 256 : 128);
+      const int64_t oc = pb.swiglu ? c / 2 : c;
+      const int64_t tiles = ((pb.M + tm - 1) / tm) * ((pb.N + oc - 1) / oc) * pb.batches;
+      const int64_t units = f ? units_pair : st->sm_count;
+      const double mma_clk = (c == 256 ? 128.0 : (c == 128 ? 64.0 : 50.0)) * 4.0 * (f == 2 ? 2.0 : 1.0);
+      const double bytes = (f == 2 ? 32768.0 : 16384.0) + (f ? 128.0 : c) * 128.0;
+      const double kblock = 1.08 * (mma_clk > bytes / 50.0 ? mma_clk : bytes / 50.0);
+      const double tile_clk = k_blocks_d * kblock + (f == 2 ? 8000.0 : 0.0) + 1500.0;
+      const double t = static_cast<double>((tiles + units - 1) / units) * tile_clk;
+      if (t < best) { best = t; form = f; bn = c; }
+    };
+    const bool allow_pair = forced != HODU_B200_PATH_TENSOR_1CTA && st->sm_count >= 2;
+    const bool only_pair = forced == HODU_B200_PATH_TENSOR_2CTA || forced == HODU_B200_PATH_TENSOR_2CTA_512;
+    if (allow_pair && forced != HODU_B200_PATH_TENSOR_2CTA) consider(2, 256);
+    if (allow_pair && forced != HODU_B200_PATH_TENSOR_2CTA_512) consider(1, 256);
+    if (!only_pair) {
+      consider(0, 256);
+      if (!pb.swiglu) {
+        consider(0, 128);
+        if (!(b_cls == 1 && esize == 1)) consider(0, 64);
+      }
     }
   }
+  const bool use_pair = form != 0;
+  const int mh = form == 2 ? 2 : 1;
+  const int64_t tile_m = form == 2 ? 512 : (form == 1 ? 256 : BM);
+  const int64_t tiles_m = (pb.M + tile_m - 1) / tile_m;
   const int out_cols = pb.swiglu ? bn / 2 : bn;       // output columns per tile
   const int64_t tiles_n = (pb.N + out_cols - 1) / out_cols;
   const int64_t num_tiles = tiles_m * tiles_n * pb.batches;
@@ -858,8 +915,9 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   const uint32_t mn_per_slab = 128u / esize;
 
   OperandMap oa, ob, ob2;
-  const char* err = build_operand_map(pb.a, esize, pb.M, pb.K, /*k_is_col=*/true, bd, bd.a_stride, BM,
-                                      BM / mn_per_slab, &oa);
+  const uint32_t a_rows_staged = static_cast<uint32_t>(BM * mh);
+  const char* err = build_operand_map(pb.a, esize, pb.M, pb.K, /*k_is_col=*/true, bd, bd.a_stride, a_rows_staged,
+                                      a_rows_staged / mn_per_slab, &oa);
   if (err) { *why = err; return 1; }
   err = build_operand_map(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false, bd, bd.b_stride, b_cols_per_box,
                           b_cols_per_box / mn_per_slab, &ob);
@@ -881,7 +939,7 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   p.num_tiles = static_cast<uint32_t>(num_tiles);
   p.bk = 128u / esize;
   p.k_blocks = static_cast<uint32_t>((pb.K + p.bk - 1) / p.bk);
-  p.group_m = use_pair ? 8 : 16;
+  p.group_m = form == 2 ? 4 : (form == 1 ? 8 : 16);  // 2048 rows of A per raster group
   p.bdim1 = static_cast<uint32_t>(bd.size[1]); p.bdim2 = static_cast<uint32_t>(bd.size[2]);
 
   const uint32_t slab_bytes = 128u * p.bk;          // MN-major slab: bk rows of 128 bytes
@@ -901,7 +959,7 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
       o.desc_lo = 1u << 16; o.kstep16 = 2;
     }
   };
-  fill(p.a, oa, BM, 1);
+  fill(p.a, oa, a_rows_staged, 1);
   fill(p.b, ob, b_cols_staged, b_sources);
   // SwiGLU without the slab dimension walks gate slabs then up slabs: the producer switches
   // maps at boxes / 2, which needs an even box count -- true for every case above.
@@ -926,7 +984,7 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   cudaGetDevice(&device);
 
 #define HODU_TC(KIND, OUTE, SW) \
-  return launch_shape<KIND, OUTE, SW>(bn, use_pair, oa.map, ob.map, ob2.map, p, device, st->sm_count, stream)
+  return launch_shape<KIND, OUTE, SW>(bn, form, oa.map, ob.map, ob2.map, p, device, st->sm_count, stream)
   if (pb.swiglu) {
     if (kind != KIND_F16) { *why = "SwiGLU epilogue exists for bf16/f16 only"; return 1; }
     if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F16, OUT_BF16, true);

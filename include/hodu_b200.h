@@ -78,7 +78,8 @@ enum {
   HODU_B200_PATH_SIMT = 1,   /* generic strided CUDA-core kernel          */
   HODU_B200_PATH_TENSOR = 2, /* tcgen05 kernel; error if layout unfit     */
   HODU_B200_PATH_TENSOR_1CTA = 3, /* tcgen05, one CTA per tile, whatever the size  */
-  HODU_B200_PATH_TENSOR_2CTA = 4  /* tcgen05, CTA pair per 256x256 tile, whatever the size */
+  HODU_B200_PATH_TENSOR_2CTA = 4, /* tcgen05, CTA pair per 256x256 tile, whatever the size */
+  HODU_B200_PATH_TENSOR_2CTA_512 = 5 /* tcgen05, CTA pair per 512x256 tile, whatever the size */
 };
 
 /* Flags of hodu_b200_swiglu. */

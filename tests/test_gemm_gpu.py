@@ -73,6 +73,35 @@ def test_tensor_core_path_all_layouts(in_dt, out_dt, a_c, b_c):
         check_close(got, want, out_dt, tol)
 
 
+FORMS = [_lib.PATH_TENSOR_1CTA, _lib.PATH_TENSOR_2CTA, _lib.PATH_TENSOR_2CTA_512]
+
+
+@pytest.mark.parametrize("form", FORMS)
+@pytest.mark.parametrize("in_dt,out_dt", [(O.BF16, O.BF16), (O.F16, O.F32), (O.F8E4M3, O.BF16), (O.I8, O.I32), (O.F32, O.F32)])
+@pytest.mark.parametrize("a_c,b_c", [("c", "c"), ("c", "r"), ("r", "c"), ("r", "r")])
+def test_every_tile_form(form, in_dt, out_dt, a_c, b_c):
+    """One CTA per 128xBN tile, CTA pair per 256x256 tile, CTA pair per 512x256 tile: same
+    results, including M/N/K tails and tiles that are mostly out of range."""
+    rng = np.random.default_rng(form * 100 + in_dt)
+    for (m, k, n) in [(640, 272, 400), (512, 512, 512), (144, 128, 80), (1040, 64, 272)]:
+        a, la = operand(rng, in_dt, m, k, a_c)
+        b, lb = operand(rng, in_dt, k, n, b_c)
+        md = dot_metadata(la, lb)
+        got, taken = gpu_matmul(a, b, md, in_dt, out_dt, is_dot=True, path=form)
+        assert taken == TENSOR
+        check_close(got, O.matmul(a, b, md, in_dt, out_dt, is_dot=True), out_dt, TOL.get(in_dt, 0))
+
+
+@pytest.mark.parametrize("form", FORMS)
+def test_every_tile_form_batched(form):
+    rng = np.random.default_rng(form)
+    lshape, rshape = (3, 520, 136), (1, 136, 264)
+    a, b = rand_storage(rng, O.BF16, lshape), rand_storage(rng, O.BF16, rshape)
+    md = matmul_metadata(Layout.from_shape(lshape), Layout.from_shape(rshape), Layout.from_shape((3, 520, 264)))
+    got, _ = gpu_matmul(a, b, md, O.BF16, path=form)
+    check_close(got, O.matmul(a, b, md, O.BF16), O.BF16, 1e-2)
+
+
 @pytest.mark.parametrize("in_dt,out_dt", PAIRS + [(O.F32, O.F32), (O.I32, O.I32)])
 def test_simt_path_any_strides(in_dt, out_dt):
     """Pitches and offsets TMA cannot describe: odd extents, element offsets, padded rows."""
@@ -152,7 +181,7 @@ def test_f32_on_tensor_cores_keeps_f32_accuracy(a_c, b_c):
         a, la = operand(rng, O.F32, m, k, a_c)
         b, lb = operand(rng, O.F32, k, n, b_c)
         md = dot_metadata(la, lb)
-        for path in (TENSOR, _lib.PATH_TENSOR_2CTA):
+        for path in (TENSOR, _lib.PATH_TENSOR_2CTA, _lib.PATH_TENSOR_2CTA_512):
             got, taken = gpu_matmul(a, b, md, O.F32, is_dot=True, path=path)
             assert taken == TENSOR
             want = np.matmul(O._strided(a.reshape(-1), la.shape, la.strides, 0).astype(np.float64),

@@ -26,7 +26,8 @@ def run_swiglu(x, wg, wu, lx, lg, lu, dt, flags, path):
         taken = K.last_path()
     finally:
         K.force_path(prev)
-    assert K.last_status(0) == 0 and canary_intact(out, m * n) and taken == path
+    want_path = _lib.PATH_SIMT if path == _lib.PATH_SIMT else _lib.PATH_TENSOR
+    assert K.last_status(0) == 0 and canary_intact(out, m * n) and taken == want_path
     return from_dev(out[: m * n], dt)
 
 
@@ -50,7 +51,7 @@ def test_fused_hidden_matches_oracle(dt, weights_as_linear, flags):
         want = O.swiglu_hidden(O.widen(xb, dt), O.widen(gb, dt), O.widen(ub, dt), dt,
                                round_each_op=(flags == _lib.SWIGLU_ROUND_EACH_OP))
         wf = O.widen(want, dt).reshape(-1)
-        for path in (_lib.PATH_TENSOR, _lib.PATH_SIMT):
+        for path in (_lib.PATH_TENSOR_1CTA, _lib.PATH_TENSOR_2CTA, _lib.PATH_TENSOR_2CTA_512, _lib.PATH_SIMT):
             got = run_swiglu(xb, gs, us, lx, lg, lu, dt, flags, path)
             assert O.rel_err(O.widen(got, dt), wf) <= 1e-2
 
