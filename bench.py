@@ -202,7 +202,10 @@ def run_reference_arm(args):
 class Workload:
     """Device-resident operands of one configuration plus the call that runs one step."""
 
-    def __init__(self, name: str, dev, stream_ptr: int):
+    def __init__(self, name: str, dev, stream_ptr: int, shard=(0, 1)):
+        """shard = (rank, world): with world > 1 this rank keeps only its slice of the fixed
+        problem -- whole batches for c2, rows of A / tokens for c3, c4, c5 (B and the weights stay
+        whole on every rank) -- which is the sharding the configurations name ("strong" scaling)."""
         import torch
         from hodu_b200 import DType, Layout
         from hodu_b200 import kernels as K
@@ -218,18 +221,25 @@ class Workload:
             t = torch.from_numpy(x32).pin_memory().to(dev, non_blocking=True)
             return Tensor.from_torch(t).to_dtype(dt).storage
 
+        from hodu_b200.dist import shard_range
+        rank, world = shard
         if name == "c2":
             c = S.config2()
+            lo, hi = shard_range(c["a"].shape[0], rank, world)
+            c = {"a": c["a"][lo:hi], "b": c["b"][lo:hi]}
             self.a, self.b = cast_on_device(c["a"], DType.BF16), cast_on_device(c["b"], DType.BF16)
             lay = Layout.from_shape(c["a"].shape)
             self.md = matmul_metadata(lay, lay, lay)
             self.out = torch.empty(lay.size(), dtype=torch.bfloat16, device=dev)
-            self.flops, self.dtype, self.launches = float(S.FLOPS[2]), "bf16", 1
+            self.flops, self.dtype, self.launches = float(S.FLOPS[2]) * (hi - lo) / 16.0, "bf16", 1
             self.in_dt, self.out_dt, self.scales, self.is_dot = DType.BF16, DType.BF16, (1.0, 1.0), False
             self.step = lambda: K.call_ops_matmul(K.matmul.BF16, d0, self.a.data_ptr(), self.b.data_ptr(),
                                                   self.out.data_ptr(), self.md, stream_ptr)
         elif name in ("c3", "c4", "c1"):
             c = {"c3": S.config3, "c4": S.config4, "c1": S.config1}[name]()
+            if name != "c1":
+                lo, hi = shard_range(c["a"].shape[0], rank, world)
+                c["a"] = np.ascontiguousarray(c["a"][lo:hi])
             if name == "c3":
                 self.a, self.b = cast_on_device(c["a"], DType.F8E4M3), cast_on_device(c["b"], DType.F8E4M3)
                 self.in_dt, self.out_dt, self.scales, self.dtype = DType.F8E4M3, DType.BF16, (c["scale_a"], c["scale_b"]), "f8e4m3"
@@ -250,11 +260,13 @@ class Workload:
                                                      stream_ptr, is_dot=True)
         elif name == "c5":
             c = S.config5()
+            lo, hi = shard_range(c["x"].shape[0], rank, world)
+            c["x"] = np.ascontiguousarray(c["x"][lo:hi])
             x = Tensor(cast_on_device(c["x"], DType.BF16), Layout.from_shape(c["x"].shape))
             lin = lambda w: Linear(Tensor(cast_on_device(np.ascontiguousarray(w.T), DType.BF16), Layout.from_shape(w.T.shape)))
             self.mlp = SwiGluMlp(lin(c["w_gate"]), lin(c["w_up"]), lin(c["w_down"]))
             self.x = x
-            self.flops, self.dtype, self.launches = float(S.FLOPS[5]), "bf16", 2
+            self.flops, self.dtype, self.launches = float(S.FLOPS[5]) * (hi - lo) / 16384.0, "bf16", 2
             self.step = lambda: self.mlp.forward(self.x)
             self.md = None
         else:
@@ -277,6 +289,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU runs the whole configuration; strong: the one configuration is sharded over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -302,7 +316,8 @@ def main():
 
     warmup = max(3, args.warmup)
     stream = torch.cuda.current_stream(dev)
-    wl = Workload(args.workload, dev, stream.cuda_stream)
+    strong = args.scaling == "strong" and world > 1
+    wl = Workload(args.workload, dev, stream.cuda_stream, shard=(rank, world) if strong else (0, 1))
     for _ in range(warmup):
         wl.step()
     torch.cuda.synchronize(dev)
@@ -332,7 +347,11 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
     ms_per_step = ms_max / args.steps
-    value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
+    fl = torch.tensor([wl.flops], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(fl, op=dist.ReduceOp.SUM)
+    total_flops = float(fl.item())  # units all ranks process per step
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- e2e through the host-buffer entry point ------------------------------------------------
     e2e = None
@@ -353,7 +372,7 @@ def main():
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item()) / n_e2e
-        e2e = {"value": wl.flops * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(ha.numel() + hb.numel()), "d2h_bytes_per_step": int(ho.numel()),
                "ms_per_step": e2e_ms, "steps": n_e2e,
                "api": "hodu_b200_matmul_host / hodu_b200_dot_host (pinned host operands, host result; wall clock around the blocking call)"}
@@ -377,8 +396,10 @@ def main():
     line = {
         "metric": "matmul throughput", "value": value, "unit": "TFLOP/s" if args.workload != "c4" else "TOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload], "per_gpu": "the whole configuration on every GPU (independent batches / rows, no collective)",
+        "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": WORKLOADS[args.workload],
+                   "per_gpu": ("1/N of the configuration: whole batches (c2) or rows of A / tokens, B and weights replicated, no collective"
+                               if strong else "the whole configuration on every GPU (independent batches / rows, no collective)"),
                    "l2": "operands + output exceed the 126 MB L2 (no flush needed)" if args.workload != "c1" else "fits in L2 (latency-bound case)",
                    "timing": "CUDA events on the launching stream around all timed steps, max over ranks"},
         "clocks": clocks.summary(),
