@@ -41,7 +41,10 @@ constexpr int BM = 128;                 // rows of A one CTA stages == TMEM lane
 constexpr int kHalfA = BM * 128;        // bytes: 128 rows (or M elements) x 128 B of K
 // 7 warps (see the role table above); with two M-halves per CTA a second group of four
 // epilogue warps (7..10) drains the second accumulator.
-constexpr int threads_for(int mh) { return 224 + 128 * (mh - 1); }
+// and, since that form cannot hide its epilogue behind the next tile, two groups of four warps
+// per accumulator (each group drains half of the columns): 3 + 16 warps.
+constexpr int epi_col_groups(int mh) { return mh == 2 ? 2 : 1; }
+constexpr int threads_for(int mh) { return 96 + 128 * mh * epi_col_groups(mh); }
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, OUT_I8 = 5 };
@@ -363,7 +366,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tail->tmem_full[i]), 1);
-      mbar_init(smem_u32(&tail->tmem_empty[i]), 4 * CG);  // one arrive per epilogue warp
+      mbar_init(smem_u32(&tail->tmem_empty[i]), 4 * CG * epi_col_groups(MH));  // one arrive per epilogue warp
     }
     mbar_init(smem_u32(&tail->drain), 1);
     tail->abort_flag = 0;
@@ -406,75 +409,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #ifdef HODU_TC_PROFILE
       long long prof_full = 0;
 #endif
-      // Issuing an MMA waits until the one before it has started, so the only slack for the
-      // per-stage bookkeeping (commit, barrier wait, fence) is the last MMA of a stage.  With one
-      // accumulator per CTA the wait for the NEXT stage is probed before that last MMA is
-      // issued (measured +2 %; with two accumulators per CTA it measured -2 % and is left out).
-      bool next_ready = false;
+      // This one thread's instruction stream bounds the main loop (with loads switched off the
+      // kernel takes the same number of cycles), so the loop is kept to: one barrier wait, one
+      // fence, one asm block of four MMAs per accumulator, one commit.  Everything else -- the
+      // descriptor bases per stage, the constant high words -- lives in registers.  (A second
+      // issuing warp for the second accumulator of the 512x256 form measured no further gain.)
+      const uint32_t a_hi = p.a.desc_hi, b_hi = p.b.desc_hi;
+      const uint32_t a_step = p.a.kstep16, b_step = p.b.kstep16;
+      const uint32_t a_lo0 = (smem_a >> 4) | p.a.desc_lo, b_lo0 = (smem_b >> 4) | p.b.desc_lo;
+      const uint32_t idesc = p.idesc, k_blocks = p.k_blocks;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;  // descriptor low words of the current stage
+      uint32_t full_bar = smem_u32(&tail->full[0]), empty_bar = smem_u32(&tail->empty[0]);
       for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step, ++lt) {
         // MH == 1: the two accumulators alternate between tiles (double buffer).
         // MH == 2: one tile fills both, accumulator h holding M-half h.
-        const uint32_t acc0 = MH == 2 ? 0u : (lt & 1u);
+        const uint32_t acc = MH == 2 ? 0u : (lt & 1u);
         const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
-        for (uint32_t kb = 0; ok && kb < p.k_blocks; ++kb) {
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
 #ifdef HODU_TC_PROFILE
           const long long tw = clock64();
 #endif
-          if (!next_ready)
-            ok = wait_bounded(smem_u32(&tail->full[s]), ph, abort_flag, p.status, code_base | 3u);
+          ok = wait_bounded(full_bar, ph, abort_flag, p.status, code_base | 3u);
 #ifdef HODU_TC_PROFILE
           prof_full += clock64() - tw;
 #endif
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t ns = (s + 1 == kStages) ? 0u : s + 1u;
-          const uint32_t nph = (s + 1 == kStages) ? ph ^ 1u : ph;
-#ifdef HODU_TC_PROFILE
-          if (p.out_vec_ok & 4u) {  // experiment: loads only, no MMAs
-            mbar_arrive(smem_u32(&tail->empty[s]));
-            if (PAIR) mbar_arrive_cluster_addr(mapa_shared(smem_u32(&tail->empty[s]), 1u));
-            if (++s == kStages) { s = 0; ph ^= 1u; }
-            continue;
-          }
-#endif
-          const uint32_t b16 = (smem_b + s * kStageB) >> 4;
-#pragma unroll
-          for (uint32_t h = 0; h < static_cast<uint32_t>(MH); ++h) {
-            const uint32_t acc = acc0 + h;
-            if (kb == 0) {  // first write of this accumulator: the epilogue must have drained it
-              PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
+          if (kb == 0) {
+            // first write of the accumulator: the epilogue must have drained it
+            PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
+                                   code_base | 2u));
+            if (!ok) break;
+            tc_fence_after_sync();
+            umma_x4<KIND, CG>(d_tmem, a_lo, a_hi, a_step, b_lo, b_hi, b_step, idesc, 0u);
+            if constexpr (MH == 2) {
+              PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[1]), acc_ph ^ 1u, abort_flag, p.status,
                                      code_base | 2u));
               if (!ok) break;
               tc_fence_after_sync();
+              umma_x4<KIND, CG>(d_tmem + BN, a_lo + (kHalfA >> 4), a_hi, a_step, b_lo, b_hi, b_step, idesc, 0u);
             }
-            const uint32_t d_tmem = tmem_base + acc * BN;
-            const uint32_t a16 = (smem_a + s * kStageA + h * kHalfA) >> 4;
-            // Descriptor arithmetic sits between the MMA issues on purpose: an issue waits for
-            // the MMA before it to start, so these few instructions cost no tensor time, while
-            // the same work done ahead of the first MMA of a stage would.
-#pragma unroll
-            for (uint32_t k = 0; k < 4; ++k) {
-              const uint64_t adesc =
-                  (static_cast<uint64_t>(p.a.desc_hi) << 32) |
-                  static_cast<uint64_t>(((a16 + k * p.a.kstep16) & 0x3FFFu) | p.a.desc_lo);
-              const uint64_t bdesc =
-                  (static_cast<uint64_t>(p.b.desc_hi) << 32) |
-                  static_cast<uint64_t>(((b16 + k * p.b.kstep16) & 0x3FFFu) | p.b.desc_lo);
-              if constexpr (MH == 1) {  // probe the next stage while the last MMA of this one is pending
-                if (k == 3u) next_ready = mbar_test_wait(smem_u32(&tail->full[ns]), nph);
-              }
-              umma<KIND, CG>(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0u ? 1u : 0u);
-            }
-            if (kb + 1 == p.k_blocks) {  // this accumulator is complete once these MMAs retire
-              if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->tmem_full[acc]), 3);
-              else umma_commit_1cta(smem_u32(&tail->tmem_full[acc]));
-            }
+          } else {
+            umma_x4<KIND, CG>(d_tmem, a_lo, a_hi, a_step, b_lo, b_hi, b_step, idesc, 1u);
+            if constexpr (MH == 2)
+              umma_x4<KIND, CG>(d_tmem + BN, a_lo + (kHalfA >> 4), a_hi, a_step, b_lo, b_hi, b_step, idesc, 1u);
           }
-          if (!ok) break;
           // frees the stage (in both CTAs of a pair) when these MMAs retire
-          if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->empty[s]), 3);
-          else umma_commit_1cta(smem_u32(&tail->empty[s]));
-          if (++s == kStages) { s = 0; ph ^= 1u; }
+          if constexpr (PAIR) umma_commit_2cta(empty_bar, 3);
+          else umma_commit_1cta(empty_bar);
+          if (++s == kStages) {
+            s = 0; ph ^= 1u;
+            a_lo = a_lo0; b_lo = b_lo0;
+            full_bar = smem_u32(&tail->full[0]); empty_bar = smem_u32(&tail->empty[0]);
+          } else {
+            a_lo += kStageA >> 4; b_lo += kStageB >> 4;
+            full_bar += 8u; empty_bar += 8u;
+          }
+        }
+        if (!ok) break;
+        // the accumulator(s) are complete once every MMA issued so far has retired
+#pragma unroll
+        for (uint32_t h = 0; h < static_cast<uint32_t>(MH); ++h) {
+          if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->tmem_full[acc + h]), 3);
+          else umma_commit_1cta(smem_u32(&tail->tmem_full[acc + h]));
         }
       }
       PROF_DUMP(1);
@@ -489,9 +487,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, and 7..10 when MH == 2)
-    const uint32_t q = warp & 3u;            // TMEM lane quadrant this warp may read
-    const uint32_t half = warp >= 7u ? 1u : 0u;  // MH == 2: which M-half (accumulator) this warp group drains
+    // ------------------------------------------------------------ epilogue (warps 2..5, and 7..18 when MH == 2)
+    // Groups of four consecutive epilogue warps cover the four TMEM lane quadrants (warp % 4).
+    // MH == 2: groups 0,1 drain accumulator 0 (left and right half of its columns), groups 2,3
+    // accumulator 1.
+    constexpr uint32_t kColGroups = epi_col_groups(MH);
+    const uint32_t q = warp & 3u;                         // TMEM lane quadrant this warp may read
+    const uint32_t e_group = (warp < 6u ? warp - 2u : warp - 3u) >> 2;
+    const uint32_t half = e_group / kColGroups;           // which M-half (accumulator)
+    const uint32_t col_group = e_group % kColGroups;      // which share of the output columns
+    constexpr uint32_t kChunks = kOutCols / 32 / kColGroups;
     const uint32_t osz = OutBytes<OUT>::value;
     const uint32_t tmem_empty0 =
         PAIR ? mapa_shared(smem_u32(&tail->tmem_empty[0]), 0u) : smem_u32(&tail->tmem_empty[0]);
@@ -513,7 +518,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                           static_cast<unsigned long long>(row) * p.ldc + n0) * osz;
       const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
 #pragma unroll 1
-      for (uint32_t c = 0; c < kOutCols / 32; ++c) {
+      for (uint32_t c = col_group * kChunks; c < (col_group + 1u) * kChunks; ++c) {
         const uint32_t col = n0 + c * 32u;
         if (col >= p.N) break;  // uniform over the warp
         uint32_t v[32];

@@ -198,6 +198,58 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
 #undef HODU_UMMA
 }
 
+// The four MMAs of one stage into one accumulator as ONE asm block: descriptor low words are
+// (a_lo + k * a_step, b_lo + k * b_step), the high words are shared.  The issuing thread is the
+// bottleneck of the main loop (every scalar instruction of its stream is serial latency), so
+// the block spends two adds and two register-pair moves per MMA and nothing else.
+// `first` = 0 makes the first MMA overwrite the accumulator instead of adding to it.
+template <int KIND, int CTA_GROUP>
+__device__ __forceinline__ void umma_x4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t a_step,
+                                        uint32_t b_lo, uint32_t b_hi, uint32_t b_step, uint32_t idesc,
+                                        uint32_t first) {
+#define HODU_UMMA4(KSTR, GSTR)                                                                    \
+  asm volatile(                                                                                   \
+      "{\n\t"                                                                                     \
+      ".reg .pred p, t;\n\t"                                                                      \
+      ".reg .b64 da, db;\n\t"                                                                     \
+      ".reg .b32 al, bl;\n\t"                                                                     \
+      "setp.ne.b32 p, %8, 0;\n\t"                                                                 \
+      "setp.eq.u32 t, 0, 0;\n\t"                                                                  \
+      "mov.b64 da, {%1, %2};\n\t"                                                                 \
+      "mov.b64 db, {%4, %5};\n\t"                                                                 \
+      "tcgen05.mma.cta_group::" GSTR ".kind::" KSTR " [%0], da, db, %7, p;\n\t"                   \
+      "add.u32 al, %1, %3;\n\t"                                                                   \
+      "add.u32 bl, %4, %6;\n\t"                                                                   \
+      "mov.b64 da, {al, %2};\n\t"                                                                 \
+      "mov.b64 db, {bl, %5};\n\t"                                                                 \
+      "tcgen05.mma.cta_group::" GSTR ".kind::" KSTR " [%0], da, db, %7, t;\n\t"                   \
+      "add.u32 al, al, %3;\n\t"                                                                   \
+      "add.u32 bl, bl, %6;\n\t"                                                                   \
+      "mov.b64 da, {al, %2};\n\t"                                                                 \
+      "mov.b64 db, {bl, %5};\n\t"                                                                 \
+      "tcgen05.mma.cta_group::" GSTR ".kind::" KSTR " [%0], da, db, %7, t;\n\t"                   \
+      "add.u32 al, al, %3;\n\t"                                                                   \
+      "add.u32 bl, bl, %6;\n\t"                                                                   \
+      "mov.b64 da, {al, %2};\n\t"                                                                 \
+      "mov.b64 db, {bl, %5};\n\t"                                                                 \
+      "tcgen05.mma.cta_group::" GSTR ".kind::" KSTR " [%0], da, db, %7, t;\n\t"                   \
+      "}" ::"r"(d_tmem),                                                                          \
+      "r"(a_lo), "r"(a_hi), "r"(a_step), "r"(b_lo), "r"(b_hi), "r"(b_step), "r"(idesc), "r"(first) \
+      : "memory")
+  if constexpr (CTA_GROUP == 1) {
+    if constexpr (KIND == KIND_F16) HODU_UMMA4("f16", "1");
+    else if constexpr (KIND == KIND_TF32) HODU_UMMA4("tf32", "1");
+    else if constexpr (KIND == KIND_F8) HODU_UMMA4("f8f6f4", "1");
+    else HODU_UMMA4("i8", "1");
+  } else {
+    if constexpr (KIND == KIND_F16) HODU_UMMA4("f16", "2");
+    else if constexpr (KIND == KIND_TF32) HODU_UMMA4("tf32", "2");
+    else if constexpr (KIND == KIND_F8) HODU_UMMA4("f8f6f4", "2");
+    else HODU_UMMA4("i8", "2");
+  }
+#undef HODU_UMMA4
+}
+
 // Make an mbarrier of THIS CTA track completion of all MMAs issued so far by
 // this thread.
 __device__ __forceinline__ void umma_commit_1cta(uint32_t bar) {
