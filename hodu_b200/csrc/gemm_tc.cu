@@ -54,7 +54,9 @@ enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, 
 template <int BN, bool PAIR, int MH> struct TileCfg {
   static constexpr int kStageA = MH * kHalfA;
   static constexpr int kStageB = PAIR ? 128 * 128 : BN * 128;
-  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 7) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 6) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int kEpiWarps = 4 * MH * (MH == 2 ? 2 : 1);
+  static constexpr int kEpiStage = 2048;  // per epilogue warp: a 32-row x 64-byte block
   static constexpr int kTmemCols = 2 * BN;  // two accumulators: double buffer (MH 1) or the two halves (MH 2)
 };
 
@@ -241,6 +243,64 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* dst, const uint32_t (&v
       for (int j = 0; j < 32; ++j)
         if (j < ncols) dst[j] = static_cast<uint8_t>(pk[j >> 2] >> ((j & 3) * 8));
     }
+  }
+}
+
+// Coalesced form of the above for 2- and 4-byte outputs whose rows allow 16-byte stores.
+// After tcgen05.ld a lane holds 32 columns of ONE row, so a direct store instruction scatters
+// 32 lanes over 32 rows, 16 bytes each: 32 partial-sector requests per instruction, and the
+// request rate (not the bytes) made the epilogue the slowest part of a tile.  Here the warp
+// passes its 32 x 64-byte block through a 2 KB shared-memory buffer (16-byte chunks XOR-swizzled
+// by row so that both directions are bank-conflict-free) and stores it back with four lanes per
+// row: every instruction writes eight full 64-byte runs.
+//   v: the lane's 32 values (floats already scaled, or raw s32); row0: first row of this warp's
+//   32-row block; col_byte0: byte offset of the chunk in an output row.
+template <int OUT>
+__device__ __forceinline__ void store_chunk_staged(uint8_t* out_tile, unsigned long long pitch_bytes,
+                                                   uint32_t row0, uint32_t rows_total, uint32_t col_byte0,
+                                                   uint32_t row_bytes_total, const uint32_t (&v)[32],
+                                                   uint32_t stage, uint32_t lane) {
+  constexpr int kWords = OutBytes<OUT>::value == 4 ? 32 : 16;  // 32-bit words per lane per chunk
+  uint32_t pk[kWords];
+  if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) pk[j] = v[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float a = __uint_as_float(v[2 * j]), b = __uint_as_float(v[2 * j + 1]);
+      if constexpr (OUT == OUT_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(a, b);
+        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+  }
+  const uint32_t wsw = (lane >> 1) & 3u;  // swizzle of the row this lane writes
+#pragma unroll
+  for (int g = 0; g < kWords / 16; ++g) {  // groups of 64 bytes per row
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+      const uint32_t addr = stage + lane * 64u + ((j ^ wsw) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[g * 16 + 4 * j]),
+                   "r"(pk[g * 16 + 4 * j + 1]), "r"(pk[g * 16 + 4 * j + 2]), "r"(pk[g * 16 + 4 * j + 3])
+                   : "memory");
+    }
+    __syncwarp();
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+      const uint32_t r = i * 8u + (lane >> 2), seg = lane & 3u;
+      uint32_t x0, x1, x2, x3;
+      const uint32_t addr = stage + r * 64u + ((seg ^ ((r >> 1) & 3u)) << 4);
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
+      const uint32_t cb = col_byte0 + static_cast<uint32_t>(g) * 64u + seg * 16u;
+      if (row0 + r < rows_total && cb < row_bytes_total)
+        *reinterpret_cast<uint4*>(out_tile + static_cast<unsigned long long>(row0 + r) * pitch_bytes + cb) =
+            make_uint4(x0, x1, x2, x3);
+    }
+    __syncwarp();
   }
 }
 
@@ -497,6 +557,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t half = e_group / kColGroups;           // which M-half (accumulator)
     const uint32_t col_group = e_group % kColGroups;      // which share of the output columns
     constexpr uint32_t kChunks = kOutCols / 32 / kColGroups;
+    const uint32_t e_warp = warp < 6u ? warp - 2u : warp - 3u;  // index among the epilogue warps
+    const uint32_t stage_buf = base_u32 + kStages * (kStageA + kStageB) + 256u + e_warp * Cfg::kEpiStage;
+    constexpr bool kStaged = (OUT == OUT_F32 || OUT == OUT_I32 || OUT == OUT_BF16 || OUT == OUT_F16);
     const uint32_t osz = OutBytes<OUT>::value;
     const uint32_t tmem_empty0 =
         PAIR ? mapa_shared(smem_u32(&tail->tmem_empty[0]), 0u) : smem_u32(&tail->tmem_empty[0]);
@@ -509,6 +572,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+#ifdef HODU_TC_PROFILE
+      const long long epi_t0 = clock64();
+#endif
       const TileCoord tc = decode_tile(p, t);
       const uint32_t row = tc.mt * kTileM + rank * 128u * MH + half * 128u + q * 32u + lane;
       const uint32_t n0 = tc.nt * kOutCols;
@@ -522,6 +588,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t col = n0 + c * 32u;
         if (col >= p.N) break;  // uniform over the warp
         uint32_t v[32];
+#ifdef HODU_TC_PROFILE
+        const long long ld_t0 = clock64();
+#endif
         tmem_ld_32x32(t_row + c * 32u, v);
         if constexpr (SWIGLU) {
           uint32_t u[32];
@@ -542,6 +611,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           tmem_wait_ld();
+#ifdef HODU_TC_PROFILE
+          if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[16 + blockIdx.x * 2] += clock64() - ld_t0;
+#endif
           if constexpr (!kIntAcc) {
             if (p.alpha != 1.0f) {
 #pragma unroll
@@ -549,10 +621,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         }
-        if (row_ok) {
+#ifdef HODU_TC_PROFILE
+        if (p.out_vec_ok & 8u) continue;  // experiment: no global stores
+#endif
+        if (kStaged && (p.out_vec_ok & 1u)) {  // uniform over the warp
+          uint8_t* out_tile = static_cast<uint8_t*>(p.out) +
+                              static_cast<unsigned long long>(tc.batch) * p.out_batch_stride * osz;
+          store_chunk_staged<OUT>(out_tile, p.ldc * osz, row - lane, p.M, col * osz,
+                                  p.N * osz, v, stage_buf, lane);
+        } else if (row_ok) {
           const int ncols = static_cast<int>(min(32u, p.N - col));
           store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
-                               p.out_vec_ok != 0u);
+                               (p.out_vec_ok & 1u) != 0u);
         }
       }
       tc_fence_before_sync();
@@ -561,6 +641,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if constexpr (PAIR) mbar_arrive_cluster_addr(tmem_empty0 + acc * 8u);
         else mbar_arrive(tmem_empty0 + acc * 8u);
       }
+#ifdef HODU_TC_PROFILE
+      if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2 + 1] += clock64() - epi_t0;
+#endif
     }
   }
 
@@ -764,7 +847,9 @@ template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
 int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
                 const TcParams& p, int device, int sm_count, cudaStream_t stream) {
   using Cfg = TileCfg<BN, PAIR, MH>;
-  constexpr size_t smem = Cfg::kStages * (Cfg::kStageA + Cfg::kStageB) + sizeof(SmemTail) + 1024;
+  constexpr size_t smem = Cfg::kStages * (Cfg::kStageA + Cfg::kStageB) + 256 /* SmemTail */ +
+                          Cfg::kEpiWarps * Cfg::kEpiStage + 1024;
+  static_assert(sizeof(SmemTail) <= 256, "barrier block outgrew its slot");
   static int max_ctas[kMaxDevices] = {0};  // CTAs (1-CTA form) or CTA pairs that can be resident
   auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU, PAIR, MH>;
   cudaLaunchConfig_t cfg = {};
@@ -982,7 +1067,7 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   p.out_vec_ok = (reinterpret_cast<uintptr_t>(pb.out) % 16 == 0 && (pb.N * osz) % 16 == 0 &&
                   (p.out_batch_stride * osz) % 16 == 0) ? 1u : 0u;
 #ifdef HODU_TC_PROFILE
-  if (const char* e = getenv("HODU_TC_EXPERIMENT")) p.out_vec_ok |= static_cast<uint32_t>(atoi(e)) & 6u;
+  if (const char* e = getenv("HODU_TC_EXPERIMENT")) p.out_vec_ok |= static_cast<uint32_t>(atoi(e)) & 14u;
 #endif
 
   int device = 0;
