@@ -253,15 +253,14 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* dst, const uint32_t (&v
 // passes its 32 x 64-byte block through a 2 KB shared-memory buffer (16-byte chunks XOR-swizzled
 // by row so that both directions are bank-conflict-free) and stores it back with four lanes per
 // row: every instruction writes eight full 64-byte runs.
-//   v: the lane's 32 values (floats already scaled, or raw s32); row0: first row of this warp's
-//   32-row block; col_byte0: byte offset of the chunk in an output row.
+//   pack_chunk turns the lane's 32 values (floats already scaled, or raw s32) into output
+//   words; store_packed_staged writes them: row0 = first row of this warp's 32-row block,
+//   col_byte0 = byte offset of the chunk in an output row.
+template <int OUT> struct ChunkWords {  // 32-bit words one lane holds for a 32-column chunk
+  static constexpr int value = OutBytes<OUT>::value == 4 ? 32 : 16;
+};
 template <int OUT>
-__device__ __forceinline__ void store_chunk_staged(uint8_t* out_tile, unsigned long long pitch_bytes,
-                                                   uint32_t row0, uint32_t rows_total, uint32_t col_byte0,
-                                                   uint32_t row_bytes_total, const uint32_t (&v)[32],
-                                                   uint32_t stage, uint32_t lane) {
-  constexpr int kWords = OutBytes<OUT>::value == 4 ? 32 : 16;  // 32-bit words per lane per chunk
-  uint32_t pk[kWords];
+__device__ __forceinline__ void pack_chunk(const uint32_t (&v)[32], uint32_t (&pk)[ChunkWords<OUT>::value]) {
   if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) pk[j] = v[j];
@@ -278,9 +277,15 @@ __device__ __forceinline__ void store_chunk_staged(uint8_t* out_tile, unsigned l
       }
     }
   }
+}
+template <int KWORDS>
+__device__ __forceinline__ void store_packed_staged(uint8_t* out_tile, unsigned long long pitch_bytes,
+                                                    uint32_t row0, uint32_t rows_total, uint32_t col_byte0,
+                                                    uint32_t row_bytes_total, const uint32_t (&pk)[KWORDS],
+                                                    uint32_t stage, uint32_t lane) {
   const uint32_t wsw = (lane >> 1) & 3u;  // swizzle of the row this lane writes
 #pragma unroll
-  for (int g = 0; g < kWords / 16; ++g) {  // groups of 64 bytes per row
+  for (int g = 0; g < KWORDS / 16; ++g) {  // groups of 64 bytes per row
 #pragma unroll
     for (uint32_t j = 0; j < 4; ++j) {
       const uint32_t addr = stage + lane * 64u + ((j ^ wsw) << 4);
@@ -583,14 +588,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          (static_cast<unsigned long long>(tc.batch) * p.out_batch_stride +
                           static_cast<unsigned long long>(row) * p.ldc + n0) * osz;
       const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
-#pragma unroll 1
-      for (uint32_t c = col_group * kChunks; c < (col_group + 1u) * kChunks; ++c) {
-        const uint32_t col = n0 + c * 32u;
-        if (col >= p.N) break;  // uniform over the warp
-        uint32_t v[32];
-#ifdef HODU_TC_PROFILE
-        const long long ld_t0 = clock64();
-#endif
+      // Loads chunk c of this warp's rows from TMEM and applies the epilogue arithmetic; v then
+      // holds the 32 final values (floats, or raw s32).
+      auto load_chunk = [&](uint32_t c, uint32_t (&v)[32]) {
         tmem_ld_32x32(t_row + c * 32u, v);
         if constexpr (SWIGLU) {
           uint32_t u[32];
@@ -611,9 +611,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           tmem_wait_ld();
-#ifdef HODU_TC_PROFILE
-          if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[16 + blockIdx.x * 2] += clock64() - ld_t0;
-#endif
           if constexpr (!kIntAcc) {
             if (p.alpha != 1.0f) {
 #pragma unroll
@@ -621,19 +618,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         }
-#ifdef HODU_TC_PROFILE
-        if (p.out_vec_ok & 8u) continue;  // experiment: no global stores
-#endif
-        if (kStaged && (p.out_vec_ok & 1u)) {  // uniform over the warp
-          uint8_t* out_tile = static_cast<uint8_t*>(p.out) +
-                              static_cast<unsigned long long>(tc.batch) * p.out_batch_stride * osz;
-          store_chunk_staged<OUT>(out_tile, p.ldc * osz, row - lane, p.M, col * osz,
-                                  p.N * osz, v, stage_buf, lane);
-        } else if (row_ok) {
-          const int ncols = static_cast<int>(min(32u, p.N - col));
-          store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
-                               (p.out_vec_ok & 1u) != 0u);
+      };
+      uint8_t* out_tile = static_cast<uint8_t*>(p.out) +
+                          static_cast<unsigned long long>(tc.batch) * p.out_batch_stride * osz;
+      const bool staged = kStaged && (p.out_vec_ok & 1u);  // uniform over the warp
+      // The 512x256 form cannot hide its epilogue behind the next tile, so for 2-byte outputs
+      // the warp first pulls ALL its chunks out of TMEM into registers (already packed), hands
+      // the accumulator back to the MMA issuer, and only then does the global stores.
+      constexpr bool kEarlyRelease = MH == 2 && (OUT == OUT_BF16 || OUT == OUT_F16);
+      bool released = false;
+      if (kEarlyRelease && staged) {
+        uint32_t pk[kChunks][16];
+#pragma unroll
+        for (uint32_t i = 0; i < kChunks; ++i) {
+          const uint32_t c = col_group * kChunks + i;
+          if (n0 + c * 32u < p.N) {
+            uint32_t v[32];
+            load_chunk(c, v);
+            pack_chunk<OUT>(v, *reinterpret_cast<uint32_t(*)[ChunkWords<OUT>::value]>(&pk[i]));
+          }
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr(tmem_empty0 + acc * 8u);
+        released = true;
+#ifdef HODU_TC_PROFILE
+        if (!(p.out_vec_ok & 8u))
+#endif
+#pragma unroll
+        for (uint32_t i = 0; i < kChunks; ++i) {
+          const uint32_t c = col_group * kChunks + i;
+          if (n0 + c * 32u < p.N)
+            store_packed_staged<16>(out_tile, p.ldc * osz, row - lane, p.M, (n0 + c * 32u) * osz, p.N * osz,
+                                    pk[i], stage_buf, lane);
+        }
+      } else {
+#pragma unroll 1
+        for (uint32_t c = col_group * kChunks; c < (col_group + 1u) * kChunks; ++c) {
+          const uint32_t col = n0 + c * 32u;
+          if (col >= p.N) break;  // uniform over the warp
+          uint32_t v[32];
+          load_chunk(c, v);
+#ifdef HODU_TC_PROFILE
+          if (p.out_vec_ok & 8u) continue;  // experiment: no global stores
+#endif
+          if (staged) {
+            if constexpr (kStaged) {
+              uint32_t pk[ChunkWords<OUT>::value];
+              pack_chunk<OUT>(v, pk);
+              store_packed_staged<ChunkWords<OUT>::value>(out_tile, p.ldc * osz, row - lane, p.M, col * osz,
+                                                          p.N * osz, pk, stage_buf, lane);
+            }
+          } else if (row_ok) {
+            const int ncols = static_cast<int>(min(32u, p.N - col));
+            store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
+                                 (p.out_vec_ok & 1u) != 0u);
+          }
+        }
+      }
+      if (released) {
+#ifdef HODU_TC_PROFILE
+        if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2 + 1] += clock64() - epi_t0;
+#endif
+        continue;
       }
       tc_fence_before_sync();
       __syncwarp();
