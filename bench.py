@@ -43,7 +43,7 @@ WORKLOADS = {
 }
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"c2": 374.7e6, "c3": 487.6e6, "c4": 647.4e6, "c5": None, "c1": None}  # profiles/gemm_tc_pair512_configs2_3_4.md
+NCU_TRAFFIC_BYTES = {"c2": 402.4e6, "c3": 541.3e6, "c4": 666.0e6, "c5": None, "c1": None}  # profiles/gemm_tc_pair512_configs2_3_4.md
 NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0}
 
 

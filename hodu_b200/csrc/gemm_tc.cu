@@ -3,14 +3,17 @@
 // `hodu_cuda_matmul_*` / `hodu_cuda_dot_*`
 // (crates/hodu_cuda_kernels/kernels/ops_matrix.cu:9-102,104-165).
 //
-// Shape of one CTA (224 threads, one CTA per SM, persistent over output tiles):
+// Shape of one CTA (one CTA per SM, persistent over output tiles; 224 threads, or 608 in
+// the 512 x 256 pair form):
 //   warp 0      TMA producer of A: 128-byte-swizzled operand tiles into a ring of stages
 //   warp 6      TMA producer of B (its own barrier arrive, so neither operand waits on the other)
-//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane)
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator, scale/convert, global store
-// The accumulator tile (128 x BN, f32 or s32) lives in TMEM and is double buffered,
-// so the epilogue of tile i overlaps the main loop of tile i+1.  Large problems run as
-// CTA pairs on 256 x 256 tiles (cta_group::2), see gemm_tc_kernel.
+//   warp 1      allocates TMEM; one elected lane issues tcgen05.mma, four per asm block
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator, scale/convert, stores staged through
+//   (+ 7..18)   swizzled shared memory so that each store instruction writes whole row pieces
+// Three tile forms: one CTA per 128 x BN tile with a double-buffered accumulator in TMEM (the
+// epilogue of tile i overlaps the main loop of tile i+1); a CTA pair (cta_group::2) per
+// 256 x 256 tile, also double buffered; a CTA pair per 512 x 256 tile, whose two accumulators
+// fill TMEM and whose sixteen epilogue warps hand them back before their global stores.
 //
 // Operand layouts: each of A and B may be K-major (K contiguous) or MN-major
 // (M resp. N contiguous); both are described to the tensor core through the
@@ -39,10 +42,9 @@ namespace {
 
 constexpr int BM = 128;                 // rows of A one CTA stages == TMEM lanes
 constexpr int kHalfA = BM * 128;        // bytes: 128 rows (or M elements) x 128 B of K
-// 7 warps (see the role table above); with two M-halves per CTA a second group of four
-// epilogue warps (7..10) drains the second accumulator.
-// and, since that form cannot hide its epilogue behind the next tile, two groups of four warps
-// per accumulator (each group drains half of the columns): 3 + 16 warps.
+// Threads = 3 warps (two producers, the MMA issuer) + the epilogue warps: four per 128-row
+// accumulator, and in the 512 x 256 form, which cannot hide its epilogue behind the next tile,
+// two such groups per accumulator, each draining half of the columns (16 epilogue warps).
 constexpr int epi_col_groups(int mh) { return mh == 2 ? 2 : 1; }
 constexpr int threads_for(int mh) { return 96 + 128 * mh * epi_col_groups(mh); }
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
