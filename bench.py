@@ -40,10 +40,15 @@ WORKLOADS = {
     "c3": "f8e4m3 matmul A[8192,8192] @ B[8192,8192], scales 1/64 -> bf16 (config 3)",
     "c4": "i8 matmul A[8192,8192] @ B[8192,8192] -> i32 (config 4)",
     "c5": "SwiGLU MLP X[16384,4096], W_gate/W_up [4096,14336], W_down [14336,4096] bf16 (config 5)",
+    "cast_bf16": "cast f32 -> bf16 of 67,108,864 contiguous elements (input preparation of one config 2 operand)",
+    "cast_e4m3": "cast f32 -> f8e4m3 of 67,108,864 contiguous elements (input preparation of one config 3 operand)",
 }
+CAST_WORKLOADS = {"cast_bf16": ("bf16", 2), "cast_e4m3": ("f8e4m3", 1)}  # destination dtype, its size
+CAST_ELEMS = 67_108_864
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"c2": 402.4e6, "c3": 541.3e6, "c4": 666.0e6, "c5": None, "c1": None}  # profiles/gemm_tc_pair512_configs2_3_4.md
+NCU_TRAFFIC_BYTES = {"c2": 402.4e6, "c3": 541.3e6, "c4": 666.0e6, "c5": None, "c1": None,  # profiles/gemm_tc_pair512_configs2_3_4.md
+                     "cast_bf16": None, "cast_e4m3": None}
 NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0}
 
 
@@ -170,28 +175,68 @@ def cpu_reference_rate(workload: str, budget_s: float):
     return flops / t / 1e12, kind, cores, sample, t
 
 
+def cpu_reference_cast_rate(workload: str, budget_s: float):
+    """Times the reference's CPU cast (oracle/_ref: hodu_cpu_cast_f32_to_{bf16,f8e4m3}; the oracle's
+    numpy codec if _ref is absent) on a bounded sample.  Returns (GB/s, kind, cores, sample, seconds)."""
+    from hodu_b200.layout import Layout
+    from hodu_b200.op_metadatas import cast_metadata
+    from oracle import oracle as O
+
+    dst_name, dst_size = CAST_WORKLOADS[workload]
+    ref = O.ref()
+    n = 1 << 22
+    x = np.random.default_rng(0).standard_normal(n, dtype=np.float32)
+    out = np.empty(n, dtype=np.uint16 if dst_size == 2 else np.uint8)
+    md = cast_metadata(Layout.from_shape((n,)))
+
+    def run():
+        t0 = time.perf_counter()
+        if ref is not None:
+            ref.cast(f"hodu_cpu_cast_f32_to_{dst_name}", x, out, md)
+        else:
+            O.narrow(x, O.BF16 if dst_name == "bf16" else O.F8E4M3)
+        return time.perf_counter() - t0
+
+    run()
+    reps, total = 0, 0.0
+    while total < min(budget_s, 5.0) and reps < 200:
+        total += run()
+        reps += 1
+    secs = total / reps
+    # the reference's cast spawns min(online CPUs, elements / 100000) pthreads per call
+    cores = min(os.cpu_count() or 1, n // 100000) if ref is not None else 1
+    return (n * (4 + dst_size) / secs / 1e9, "reference" if ref is not None else "port", cores,
+            f"{n} of {CAST_ELEMS} elements, mean of {reps} calls", secs)
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     per_step = max(0.05, min(3.0, 120.0 / max(1, args.steps + args.warmup)))
+    is_cast = args.workload in CAST_WORKLOADS
+    rate = cpu_reference_cast_rate if is_cast else cpu_reference_rate
+    unit = "GB/s" if is_cast else "TFLOP/s"
     for _ in range(args.warmup):
-        cpu_reference_rate(args.workload, per_step)
+        rate(args.workload, per_step)
     vals, secs = [], []
     sample = kind = ""
     cores = 1
     for _ in range(args.steps):
-        v, kind, cores, sample, t = cpu_reference_rate(args.workload, per_step)
+        v, kind, cores, sample, t = rate(args.workload, per_step)
         vals.append(v)
         secs.append(t)
     value = statistics.mean(vals)
     line = {
-        "impl": "reference", "metric": "matmul throughput", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": "cast throughput" if is_cast else "matmul throughput", "value": value,
+        "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload], "note": "reference CPU path (hodu_cpu_kernels C kernel over OpenBLAS sgemm) on host cores; each step is a bounded sample"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
-        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": WORKLOADS[args.workload],
+                   "note": ("reference CPU cast kernel (hodu_cpu_kernels ops_cast.c, its own pthreads) on host cores; each step is a bounded sample" if is_cast else
+                            "reference CPU path (hodu_cpu_kernels C kernel over OpenBLAS sgemm) on host cores; each step is a bounded sample")},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -269,6 +314,18 @@ class Workload:
             self.flops, self.dtype, self.launches = float(S.FLOPS[5]) * (hi - lo) / 16384.0, "bf16", 2
             self.step = lambda: self.mlp.forward(self.x)
             self.md = None
+        elif name in CAST_WORKLOADS:
+            # HBM-bound leg: algorithmic bytes per element = 4 (f32 read) + size of the destination.
+            dst_name, dst_size = CAST_WORKLOADS[name]
+            dst_dt = {"bf16": DType.BF16, "f8e4m3": DType.F8E4M3}[dst_name]
+            g = torch.Generator(device=dev).manual_seed(7)
+            self.a = torch.randn(CAST_ELEMS, generator=g, device=dev, dtype=torch.float32)
+            from hodu_b200.dtype import to_torch
+            self.out = torch.empty(CAST_ELEMS, dtype=to_torch(dst_dt), device=dev)
+            self.md = cast_metadata(Layout.from_shape((CAST_ELEMS,)))
+            kern = getattr(K.cast, f"F32_{dst_name.upper()}")
+            self.flops, self.dtype, self.launches = float(CAST_ELEMS) * (4 + dst_size), f"f32->{dst_name}", 1
+            self.step = lambda: K.call_ops_cast(kern, d0, self.a.data_ptr(), self.out.data_ptr(), self.md, stream_ptr)
         else:
             raise SystemExit(f"unknown workload {name}")
 
@@ -351,7 +408,9 @@ def main():
     if world > 1:
         dist.all_reduce(fl, op=dist.ReduceOp.SUM)
     total_flops = float(fl.item())  # units all ranks process per step
-    value = total_flops / (ms_per_step * 1e-3) / 1e12
+    is_cast = args.workload in CAST_WORKLOADS
+    per_unit = 1e9 if is_cast else 1e12   # casts count bytes (GB/s), products count flops (TFLOP/s)
+    value = total_flops / (ms_per_step * 1e-3) / per_unit
 
     # ---- e2e through the host-buffer entry point ------------------------------------------------
     e2e = None
@@ -384,7 +443,10 @@ def main():
 
     peaks = measured_peaks()
     timed_s = ms_total * 1e-3
-    if args.workload in ("c2", "c5"):
+    if is_cast:
+        peak, peak_src = peaks["hbm_gbs"], (f"{peaks['source']} copy bandwidth (MEASURED_PEAKS.json)"
+                                            if peaks["source"] == "measured" else "fallback 6650 GB/s")
+    elif args.workload in ("c2", "c5"):
         # cuBLAS burst for a short region at full clocks; its sustained figure once the region is
         # long or the power cap was seen active while it ran
         clk = clocks.summary()
@@ -392,9 +454,10 @@ def main():
         peak, peak_src = peaks[peak_kind], f"{peaks['source']} cuBLAS bf16 {peak_kind} (MEASURED_PEAKS.json)" if peaks["source"] == "measured" else "fallback 1590 burst / 1400 sustained"
     else:
         peak, peak_src = NOMINAL_PEAK_TFLOPS[args.workload], "nominal dense peak for this dtype (no measured figure for it)"
-    achieved = wl.flops / (ms_total / args.steps * 1e-3) / 1e12  # this rank, per launch group
+    achieved = wl.flops / (ms_total / args.steps * 1e-3) / per_unit  # this rank, per launch group
+    unit = "GB/s" if is_cast else ("TFLOP/s" if args.workload != "c4" else "TOP/s")
     line = {
-        "metric": "matmul throughput", "value": value, "unit": "TFLOP/s" if args.workload != "c4" else "TOP/s",
+        "metric": "cast throughput" if is_cast else "matmul throughput", "value": value, "unit": unit,
         "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
         "config": {"workload": WORKLOADS[args.workload],
@@ -404,15 +467,20 @@ def main():
                    "timing": "CUDA events on the launching stream around all timed steps, max over ranks"},
         "clocks": clocks.summary(),
         "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES[args.workload], "peak_source": peak_src,
-                     "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS[args.workload]},
+        "roofline": {"bound": "hbm" if is_cast else "tensor", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s" if is_cast else "TFLOP/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES[args.workload], "peak_source": peak_src},
     }
+    if is_cast:
+        line["roofline"]["algorithmic_bytes_per_launch"] = wl.flops
+    else:
+        line["roofline"]["frac_of_nominal"] = achieved / NOMINAL_PEAK_TFLOPS[args.workload]
     if e2e is not None:
         line["e2e"] = e2e
     if world == 1 and not args.no_cpu_baseline:
-        v, kind, cores, sample, secs = cpu_reference_rate(args.workload, 15.0)
-        line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample, "seconds": secs}
+        v, kind, cores, sample, secs = (cpu_reference_cast_rate if is_cast else cpu_reference_rate)(args.workload, 15.0)
+        line["cpu_baseline"] = {"value": v, "unit": "GB/s" if is_cast else "TFLOP/s", "cores": cores, "kind": kind,
+                                "sample": sample, "seconds": secs}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

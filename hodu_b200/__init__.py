@@ -6,6 +6,7 @@ the benchmark:
 
   kernels        the `hodu_cuda_kernels` launch wrappers (call_ops_matmul / dot / cast)
   op_metadatas   the metadata wire formats
+  einsum         the einsum equation parser and its wire format
   layout, dtype  `Layout`, `DType`
   tensor         `Tensor::matmul` / `dot` / `transpose` / `to_dtype` (needs torch + CUDA)
   nn             `Linear`, SwiGLU MLP

@@ -24,6 +24,8 @@ SIGNATURES = {
     "hodu_b200_cast": (_i, [_i, _vp, _u8, _u8, _vp, _vp, _szp, _sz]),
     "hodu_b200_contiguous": (_i, [_i, _vp, _u8, _vp, _vp, _szp, _sz]),
     "hodu_b200_swiglu": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
+    "hodu_b200_linear": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
+    "hodu_b200_einsum": (_i, [_i, _vp, _u8, C.POINTER(C.c_void_p), _sz, _vp, _szp, _sz]),
     "hodu_b200_matmul_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_f32_static": (_i, [_i, _vp, _vp, _vp, _vp, _szp, _sz]),
@@ -39,6 +41,7 @@ SIGNATURES = {
 
 PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_TENSOR_1CTA, PATH_TENSOR_2CTA, PATH_TENSOR_2CTA_512 = 0, 1, 2, 3, 4, 5
 SWIGLU_ROUND_EACH_OP, SWIGLU_ROUND_ONCE = 0, 1
+LINEAR_ROUND_EACH_OP, LINEAR_ROUND_ONCE = 0, 1
 
 
 class CudaKernelError(RuntimeError):

@@ -338,6 +338,54 @@ int hodu_b200_swiglu(int device, void* stream, uint8_t dtype, const void* x, con
   return run_problem(pb, st, static_cast<cudaStream_t>(stream));
 }
 
+int hodu_b200_linear(int device, void* stream, uint8_t dtype, const void* x, const void* w,
+                     const void* bias, void* out, const size_t* md, size_t len, uint32_t flags) {
+  if (dtype != HODU_DTYPE_BF16 && dtype != HODU_DTYPE_F16 && dtype != HODU_DTYPE_F32)
+    return fail(HODU_B200_ERR_INVALID_KERNEL, "linear: unsupported dtype %s", dtype_name(dtype));
+  if (flags != HODU_B200_LINEAR_ROUND_EACH_OP && flags != HODU_B200_LINEAR_ROUND_ONCE)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "linear: unknown flags %u", flags);
+  if (!md || len < 2) return fail(HODU_B200_ERR_INVALID_INPUT, "linear: metadata too short (%zu)", len);
+  Problem pb;
+  int r = parse_matmul(md, len - 2, &pb);
+  if (r) return r;
+  if (pb.M == 0 || pb.N == 0 || pb.batches == 0) return 0;
+  if (!x || !w || !out) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+  pb.in_dtype = dtype; pb.out_dtype = dtype;
+  pb.a.ptr = x; pb.b.ptr = w; pb.out = out;
+  pb.bias = bias;
+  pb.bias_stride = static_cast<int64_t>(md[len - 2]);
+  pb.bias_offset = static_cast<int64_t>(md[len - 1]);
+  pb.bias_flags = flags;
+  if (pb.K == 0 && bias)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "linear: in_features == 0 with a bias is not supported");
+  return run_problem(pb, st, static_cast<cudaStream_t>(stream));
+}
+
+int hodu_b200_einsum(int device, void* stream, uint8_t dtype, const void* const* inputs,
+                     size_t num_inputs, void* out, const size_t* md, size_t len) {
+  if (!in_out_pair_ok(dtype, dtype))
+    return fail(HODU_B200_ERR_INVALID_KERNEL, "einsum: unsupported dtype %s", dtype_name(dtype));
+  Problem pb;
+  bool swapped = false;
+  const int r = parse_einsum(md, len, num_inputs, &pb, &swapped);
+  if (r) return r;
+  if (pb.M == 0 || pb.N == 0 || pb.batches == 0) return 0;
+  if (!inputs || !inputs[0] || !inputs[1] || !out) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+  pb.in_dtype = dtype; pb.out_dtype = dtype;
+  pb.a.ptr = inputs[swapped ? 1 : 0];
+  pb.b.ptr = inputs[swapped ? 0 : 1];
+  pb.out = out;
+  return run_problem(pb, st, static_cast<cudaStream_t>(stream));
+}
+
 const char* hodu_b200_strerror(int code) {
   switch (code) {
     case HODU_B200_OK: return "ok";

@@ -81,6 +81,12 @@ struct Problem {
   uint32_t swiglu_flags = 0;
   void* out = nullptr;   // contiguous [batches, M, N]
   float alpha = 1.0f;    // scale_lhs * scale_rhs
+  // Bias of a Linear layer: [N] values of the OUTPUT dtype added to every output row
+  // (hodu_nn/src/modules/linear.rs:38-47).  `bias_flags` says whether the product is rounded
+  // to the output dtype before the addition (what the reference's two ops do) or only after.
+  const void* bias = nullptr;
+  int64_t bias_offset = 0, bias_stride = 1;
+  uint32_t bias_flags = 0;
   bool f32_presplit = false;  // f32 operands already in the three-segment TF32 split form (gemm_f32.cu)
 };
 
@@ -105,6 +111,9 @@ int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t lim
 // Parsers of the reference's wire formats and the path chooser (api.cu).
 int parse_matmul(const size_t* md, size_t len, Problem* pb);
 int parse_dot(const size_t* md, size_t len, Problem* pb);
+// Two-operand einsum wire format -> matrix product over views (einsum.cu).  `swapped`: the
+// second einsum operand is the product's left-hand side.
+int parse_einsum(const size_t* md, size_t len, size_t num_inputs, Problem* pb, bool* swapped);
 int check_operands(int in_dtype, int out_dtype, const void* lhs, const void* rhs, void* out,
                    float scale_lhs, float scale_rhs, uint32_t epilogue);
 int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream);

@@ -35,6 +35,9 @@ struct SimtParams {
   float alpha;
   unsigned swiglu_flags;
   long long tiles_m, tiles_n;
+  const void* bias;        // [N] of TOut (offset applied), or null
+  long long bias_stride;
+  unsigned bias_flags;
 };
 
 template <typename T> struct Widen;
@@ -159,7 +162,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
           }
           O[gi * p.N + gj] = Narrow<TOut, float>::put(v);
         } else if constexpr (std::is_same<Acc, float>::value) {
-          O[gi * p.N + gj] = Narrow<TOut, Acc>::put(acc[i][j] * p.alpha);
+          float v = acc[i][j] * p.alpha;
+          if (p.bias) {
+            if (p.bias_flags == HODU_B200_LINEAR_ROUND_EACH_OP) v = Widen<TOut>::get(Narrow<TOut, float>::put(v));
+            v += Widen<TOut>::get(static_cast<const TOut*>(p.bias)[gj * p.bias_stride]);
+          }
+          O[gi * p.N + gj] = Narrow<TOut, Acc>::put(v);
         } else {
           O[gi * p.N + gj] = Narrow<TOut, Acc>::put(acc[i][j]);
         }
@@ -200,6 +208,9 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   p.bshape[15] = pb.batches;
   p.alpha = pb.alpha;
   p.swiglu_flags = pb.swiglu_flags;
+  p.bias = pb.bias ? static_cast<const uint8_t*>(pb.bias) + pb.bias_offset * dtype_size(pb.out_dtype) : nullptr;
+  p.bias_stride = pb.bias_stride;
+  p.bias_flags = pb.bias_flags;
   p.tiles_m = (pb.M + TM - 1) / TM;
   p.tiles_n = (pb.N + TN - 1) / TN;
   const long long tiles = p.tiles_m * p.tiles_n * pb.batches;

@@ -95,8 +95,11 @@ struct TcParams {
   uint32_t idesc;
   uint32_t out_vec_ok;    // rows of `out` allow 16-byte stores
   uint32_t swiglu_flags;
+  uint32_t bias_flags;
   float alpha;
   unsigned long long ldc, out_batch_stride;  // elements
+  const void* bias;       // [N] values of the output dtype added per column, or null
+  long long bias_stride;  // elements
   void* out;
   uint32_t* status;
 };
@@ -173,6 +176,12 @@ template <int OUT> __device__ __forceinline__ float round_to_storage(float x) {
   if constexpr (OUT == OUT_BF16) return __bfloat162float(__float2bfloat16_rn(x));
   else if constexpr (OUT == OUT_F16) return __half2float(__float2half_rn(x));
   else return x;
+}
+
+template <int OUT> __device__ __forceinline__ float load_bias(const void* bias, long long i) {
+  if constexpr (OUT == OUT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[i]);
+  else if constexpr (OUT == OUT_F16) return __half2float(static_cast<const __half*>(bias)[i]);
+  else return static_cast<const float*>(bias)[i];
 }
 
 template <int OUT> struct OutBytes {
@@ -617,6 +626,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (p.alpha != 1.0f) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
+            }
+            if constexpr (OUT == OUT_F32 || OUT == OUT_BF16 || OUT == OUT_F16) {
+              if (p.bias != nullptr) {  // uniform over the grid
+                // Lane l fetches the bias of column c*32 + l; the 32 values go round by shuffle.
+                const uint32_t bcol = n0 + c * 32u + lane;
+                const float mine = bcol < p.N ? load_bias<OUT>(p.bias, static_cast<long long>(bcol) * p.bias_stride) : 0.0f;
+                const bool each = (p.bias_flags == HODU_B200_LINEAR_ROUND_EACH_OP);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  float x = __uint_as_float(v[j]);
+                  if (each) x = round_to_storage<OUT>(x);
+                  v[j] = __float_as_uint(x + __shfl_sync(0xFFFFFFFFu, mine, j));
+                }
+              }
             }
           }
         }
@@ -1108,6 +1131,9 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
             (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>((use_pair ? 256 : BM) >> 4) << 24);
   p.alpha = pb.alpha;
   p.swiglu_flags = pb.swiglu_flags;
+  p.bias = pb.bias ? static_cast<const uint8_t*>(pb.bias) + pb.bias_offset * dtype_size(pb.out_dtype) : nullptr;
+  p.bias_stride = pb.bias_stride;
+  p.bias_flags = pb.bias_flags;
   p.ldc = static_cast<unsigned long long>(pb.N);
   p.out_batch_stride = static_cast<unsigned long long>(pb.M) * static_cast<unsigned long long>(pb.N);
   p.out = pb.out;

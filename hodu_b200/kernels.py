@@ -43,6 +43,7 @@ contiguous = _Family("contiguous")
 matmul = _Family("matmul")
 dot = _Family("dot")
 cast = _Family("cast")
+einsum = _Family("einsum")
 
 
 def _parse(kernel: Kernel, op: str):
@@ -104,6 +105,23 @@ def call_ops_swiglu(dtype: DType, device: int, x: int, w_gate: int, w_up: int, o
     md = metadata_array(metadata)
     check(_lib.lib().hodu_b200_swiglu(device, stream, int(dtype), x, w_gate, w_up, output, md,
                                       len(metadata), flags))
+
+
+def call_ops_linear(dtype: DType, device: int, x: int, w: int, bias: Optional[int], output: int,
+                    metadata: Sequence[int], flags: int = _lib.LINEAR_ROUND_EACH_OP, stream: int = 0) -> None:
+    """x . w + bias in one launch; `metadata` = matmul wire format + [bias_stride, bias_offset]."""
+    md = metadata_array(metadata)
+    check(_lib.lib().hodu_b200_linear(device, stream, int(dtype), x, w, bias, output, md, len(metadata), flags))
+
+
+def call_ops_einsum(kernel: Kernel, device: int, inputs: Sequence[int], output: int,
+                    metadata: Sequence[int], stream: int = 0) -> None:
+    """`call_ops_einsum` (crates/hodu_cuda_kernels/src/kernels/ops_einsum.rs:24-70) for the
+    two-operand contractions that are matrix products; other forms raise `invalid kernel`."""
+    dt = _parse(kernel, "einsum")
+    md = metadata_array(metadata)
+    ptrs = (C.c_void_p * len(inputs))(*[int(p) for p in inputs])
+    check(_lib.lib().hodu_b200_einsum(device, stream, int(dt), ptrs, len(inputs), output, md, len(metadata)))
 
 
 def call_ops_matmul_host(in_dtype: DType, out_dtype: DType, device: int, lhs_host: int, rhs_host: int,

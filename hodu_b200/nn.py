@@ -10,22 +10,42 @@ import torch
 
 from . import _lib, kernels
 from .layout import Layout
-from .op_metadatas import swiglu_metadata
+from .op_metadatas import matmul_metadata, swiglu_metadata
 from .tensor import HoduError, Tensor, _stream
 
 
 class Linear:
-    """weight is [out_features, in_features]; forward = input.matmul(weight.transpose(-2,-1))."""
+    """weight is [out_features, in_features], bias [out_features] or None;
+    forward = input.matmul(weight.transpose(-2,-1)) (+ bias), as one launch."""
 
-    def __init__(self, weight: Tensor, bias: Optional[Tensor] = None):
+    def __init__(self, weight: Tensor, bias: Optional[Tensor] = None, rounding: int = _lib.LINEAR_ROUND_EACH_OP):
         if len(weight.shape) != 2:
             raise HoduError("Linear weight must be 2-D [out, in]")
         if bias is not None:
-            raise HoduError("bias add is a separate broadcast kernel in the reference and is not on this path")
-        self.weight = weight
+            if tuple(bias.shape) != (weight.shape[0],):
+                raise HoduError(f"Linear bias must be [{weight.shape[0]}], got {tuple(bias.shape)}")
+            if bias.dtype != weight.dtype:
+                raise HoduError("Linear bias and weight must have the same dtype")
+        self.weight, self.bias, self.rounding = weight, bias, rounding
 
     def forward(self, input: Tensor) -> Tensor:
-        return input.matmul(self.weight.transpose(-2, -1))
+        wt = self.weight.transpose(-2, -1)
+        if self.bias is None:
+            return input.matmul(wt)
+        if len(input.shape) < 2 or input.shape[-1] != wt.shape[0]:
+            raise HoduError(f"incompatible shapes {input.shape} x {wt.shape}")
+        if input.dtype != self.weight.dtype:
+            raise HoduError("Linear input and weight must have the same dtype")
+        batch = tuple(input.shape[:-2])
+        out_layout = Layout.from_shape((*batch, input.shape[-2], wt.shape[1]))
+        rhs = wt.broadcast((*batch, *wt.shape)) if batch else wt
+        md = matmul_metadata(input.layout, rhs.layout, out_layout)
+        md = [*md, self.bias.layout.strides[0], self.bias.layout.offset]
+        out = torch.empty(out_layout.size(), dtype=input.storage.dtype, device=input.storage.device)
+        kernels.call_ops_linear(input.dtype, input.device_id, input.storage.data_ptr(), wt.storage.data_ptr(),
+                                self.bias.storage.data_ptr(), out.data_ptr(), md, self.rounding,
+                                _stream(input.storage.device))
+        return Tensor(out, out_layout)
 
 
 class SwiGluMlp:

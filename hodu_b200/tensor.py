@@ -173,6 +173,29 @@ class Tensor:
         return Tensor(out, Layout.from_shape(self.layout.shape))
 
 
+def einsum(equation: str, tensors: Sequence[Tensor]) -> Tensor:
+    """`Tensor::einsum` (crates/hodu_core/src/tensor/ops/einsum.rs:42-...) for the two-operand
+    contractions that are matrix products ("ij,jk->ik", "bij,bjk->bik", "bhqd,bhkd->bhqk", ...).
+    Other forms are the reference's own einsum kernel's business and raise `invalid kernel`."""
+    from .einsum import ParsedEinsum, einsum_metadata
+    if not tensors:
+        raise HoduError("einsum requires at least one tensor")
+    first = tensors[0]
+    for t in tensors[1:]:
+        _validate_pair(first, t)
+    try:
+        parsed = ParsedEinsum.parse(equation, [t.shape for t in tensors])
+    except ValueError as e:
+        raise HoduError(str(e)) from None
+    out_layout = Layout.from_shape(tuple(parsed.compute_output_shape()))
+    md = einsum_metadata(parsed, [t.layout for t in tensors], out_layout)
+    out = first._new_buffer(max(out_layout.size(), 1), None)
+    kernels.call_ops_einsum(getattr(kernels.einsum, str(first.dtype).upper()), first.device_id,
+                            [t.storage.data_ptr() for t in tensors], out.data_ptr(), md,
+                            _stream(first.storage.device))
+    return Tensor(out, out_layout)
+
+
 def matmul_vjp(a: Tensor, b: Tensor, grad_output: Tensor):
     """Vector-Jacobian products of `a.matmul(b)` as the reference computes them
     (crates/hodu_core/src/tensor/gradient/vjp_matrix.rs:17-66): dA = grad @ B^T and

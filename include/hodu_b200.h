@@ -92,6 +92,15 @@ enum {
   HODU_B200_SWIGLU_ROUND_ONCE = 1
 };
 
+/* Flags of hodu_b200_linear. */
+enum {
+  /* Round the product to the storage dtype, then add the bias and round again: what the
+   * reference's two ops (`matmul`, then `add`) produce. */
+  HODU_B200_LINEAR_ROUND_EACH_OP = 0,
+  /* Add the bias to the f32 accumulator and round once. */
+  HODU_B200_LINEAR_ROUND_ONCE = 1
+};
+
 /*
  * Per-device set-up: creates the status word and caches device properties.
  * Replaces the lazily built per-device state of the reference
@@ -182,6 +191,43 @@ int hodu_b200_contiguous(int device, void* stream, uint8_t dtype, const void* in
 int hodu_b200_swiglu(int device, void* stream, uint8_t dtype,
                      const void* x, const void* w_gate, const void* w_up, void* out,
                      const size_t* metadata, size_t metadata_len, uint32_t flags);
+
+/*
+ * Linear layer with its bias fused into the product's epilogue:
+ *   out[..., N] = x[..., K] . w[K, N] + bias[N]
+ * In the reference `Linear::forward` (crates/hodu_nn/src/modules/linear.rs:38-47) is
+ * `input.matmul(weight.transpose(-2,-1))` followed by `output.add(bias)`, a separate broadcast
+ * kernel over the whole output (crates/hodu_cuda_kernels/kernels/ops_binary.cu).
+ * metadata = the matmul wire format of hodu_b200_matmul (any batch dims on x; `w` is normally the
+ * 2-D transposed view of the [N,K] weight, strides (1,K)) followed by two more words:
+ * [bias_stride, bias_offset] in elements.  `bias` has the dtype of the output and may be null
+ * (no bias: same as hodu_b200_matmul).  dtype: bf16 | f16 | f32.
+ * `flags`: HODU_B200_LINEAR_ROUND_EACH_OP or HODU_B200_LINEAR_ROUND_ONCE.
+ */
+int hodu_b200_linear(int device, void* stream, uint8_t dtype,
+                     const void* x, const void* w, const void* bias, void* out,
+                     const size_t* metadata, size_t metadata_len, uint32_t flags);
+
+/*
+ * Two-operand einsum contractions routed to the GEMM.  Replaces, for the forms below,
+ * `call_ops_einsum` (crates/hodu_cuda_kernels/src/kernels/ops_einsum.rs:24-70) and its
+ * one-thread-per-output kernel (crates/hodu_cuda_kernels/kernels/ops_einsum.cu:76-...).
+ * metadata = the reference's einsum wire format (`einsum_metadata`,
+ * crates/hodu_core/src/op_metadatas.rs:1502-1567; restated in crates/hodu_cpu_kernels/tests/ops_einsum.rs:18-84):
+ *   [num_output_els, num_inputs, num_total_indices, num_contraction_indices, output_ndim,
+ *    output_shape.., then per input: ndim, shape.., strides.., offset, dim_to_index_id..,
+ *    contraction_index_ids.., index_sizes.., output_index_ids..]
+ * Accepted: num_inputs == 2, no index repeated within one operand, and every index of exactly
+ * one of four kinds -- batch (in both operands and the output), M (first operand and output),
+ * N (second operand and output), K (both operands, not the output) -- with the output ordered
+ * [batch.., M.., N..] or [batch.., N.., M..] (the operands are then swapped) and the indices
+ * of a kind mergeable into one stride in each operand.  That covers "ij,jk->ik", "bij,bjk->bik",
+ * "ik,jk->ij", "bhqd,bhkd->bhqk", "i,i->", "i,j->ij" and the like.  Anything else
+ * (trace, transposition, sums over one operand) returns HODU_B200_ERR_INVALID_KERNEL so the
+ * caller keeps its own kernel for it.  `inputs` is an array of `num_inputs` device pointers.
+ */
+int hodu_b200_einsum(int device, void* stream, uint8_t dtype, const void* const* inputs,
+                     size_t num_inputs, void* out, const size_t* metadata, size_t metadata_len);
 
 /*
  * Host-buffer forms: the whole of "create tensors on the device, multiply, read

@@ -75,6 +75,13 @@ class _Ref:
         fn.restype = None
         fn(_ptr(src), _ptr(dst), _md(md))
 
+    def einsum(self, name: str, inputs: Sequence[np.ndarray], out: np.ndarray, md: Sequence[int]) -> None:
+        """hodu_cpu_einsum_{dtype}(const void** inputs, void* output, const size_t* metadata)."""
+        fn = getattr(self.base, name)
+        fn.restype = None
+        ptrs = (C_.c_void_p * len(inputs))(*[a.ctypes.data for a in inputs])
+        fn(ptrs, _ptr(out), _md(md))
+
     def blas_info(self) -> dict:
         """Thread count and build string of the OpenBLAS behind hodu_cpu_{matmul,dot}_f32."""
         info = {"threads": 0, "config": "none", "path": ""}
@@ -315,6 +322,67 @@ def swiglu_hidden(x: np.ndarray, wg: np.ndarray, wu: np.ndarray, dtype: int, rou
         s = widen(narrow(silu(g), dtype), dtype)
         return narrow(s * u, dtype)
     return narrow(silu(g) * u, dtype)
+
+
+def linear(x: np.ndarray, w: np.ndarray, bias: np.ndarray, dtype: int, round_each_op: bool = True) -> np.ndarray:
+    """x[..., K] . w[K, N] + bias[N] for widened-f32 arrays holding values of storage dtype
+    `dtype` (`Linear::forward`, crates/hodu_nn/src/modules/linear.rs:38-47: `matmul`, then `add`).
+    round_each_op: the product is rounded to `dtype` before the addition, as the reference's two
+    ops do; otherwise only the sum is rounded.  Returns raw storage, flat."""
+    c = np.matmul(x, w).astype(np.float32)
+    if round_each_op:
+        c = widen(narrow(c, dtype), dtype)
+    return narrow((c + bias.astype(np.float32)).astype(np.float32), dtype).reshape(-1)
+
+
+def parse_einsum_md(md: Sequence[int]):
+    """Splits the reference's einsum wire format
+    (crates/hodu_cpu_kernels/kernels/ops_einsum.c:27-70 reads it the same way)."""
+    md = [int(v) for v in md]
+    n_out, n_in, n_idx, n_con, out_ndim = md[:5]
+    pos = 5
+    out_shape = md[pos:pos + out_ndim]; pos += out_ndim
+    inputs = []
+    for _ in range(n_in):
+        nd = md[pos]; pos += 1
+        shape = md[pos:pos + nd]; pos += nd
+        strides = md[pos:pos + nd]; pos += nd
+        off = md[pos]; pos += 1
+        ids = md[pos:pos + nd]; pos += nd
+        inputs.append((shape, strides, off, ids))
+    con = md[pos:pos + n_con]; pos += n_con
+    sizes = md[pos:pos + n_idx]; pos += n_idx
+    out_ids = md[pos:pos + out_ndim]; pos += out_ndim
+    assert pos == len(md), "einsum metadata length"
+    return n_out, out_shape, inputs, con, sizes, out_ids
+
+
+def einsum(inputs: Sequence[np.ndarray], md: Sequence[int], dtype: int) -> np.ndarray:
+    """Oracle of the einsum op for storage dtype `dtype`: every output element is the sum over
+    all contraction indices of the product of the operands' elements, accumulated in f32 and
+    converted once (crates/hodu_cpu_kernels/kernels/ops_einsum.c:134-170; the CUDA kernel
+    crates/hodu_cuda_kernels/kernels/ops_einsum.cu:126-175 does the same).  Integers: exact,
+    wrapped to the storage width.  Returns raw storage, flat."""
+    n_out, out_shape, ins, _con, _sizes, out_ids = parse_einsum_md(md)
+    views, subs = [], []
+    for flat, (shape, strides, off, ids) in zip(inputs, ins):
+        v = _strided(flat.reshape(-1), shape, strides, off)
+        if dtype in (I8, I32):
+            v = widen(np.ascontiguousarray(v), dtype).astype(np.float64)
+        else:
+            v = widen(np.ascontiguousarray(v), dtype)
+        views.append(v)
+        subs.append(list(ids))
+    args = []
+    for v, sub in zip(views, subs):
+        args += [v, sub]
+    c = np.einsum(*args, list(out_ids))
+    if dtype in (I8, I32):
+        ci = np.rint(c).astype(np.int64)
+        if dtype == I32:
+            return (ci & 0xFFFFFFFF).astype(np.uint32).view(np.int32).reshape(-1)
+        return narrow(ci, I8).reshape(-1)
+    return narrow(np.asarray(c, dtype=np.float32), dtype).reshape(-1)
 
 
 def rel_err(got_f32: np.ndarray, want_f32: np.ndarray) -> float:

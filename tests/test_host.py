@@ -141,3 +141,67 @@ def test_synthetic_inputs_are_seeded_and_shaped():
     c5 = S.config5(scale=128)
     assert c5["w_gate"].shape == (32, 112) and c5["w_down"].shape == (112, 32)
     assert S.FLOPS[2] == 274877906944 and S.FLOPS[3] == 1099511627776 and S.FLOPS[5] == 5772436045824
+
+
+# ---------------------------------------------------------------- einsum equation parser
+# Mirrors the parser tests of the reference (crates/hodu_core/src/einsum.rs:171-244).
+def test_einsum_parse_forms():
+    from hodu_b200.einsum import ParsedEinsum, einsum_metadata
+    p = ParsedEinsum.parse("ij,jk->ik", [(2, 3), (3, 4)])
+    assert p.input_subscripts == [["i", "j"], ["j", "k"]] and p.output_subscripts == ["i", "k"]
+    assert p.contraction_indices == ["j"] and p.compute_output_shape() == [2, 4]
+    p = ParsedEinsum.parse("ij->ji", [(2, 3)])
+    assert p.output_subscripts == ["j", "i"] and p.contraction_indices == [] and p.compute_output_shape() == [3, 2]
+    p = ParsedEinsum.parse("ii->", [(3, 3)])
+    assert p.output_subscripts == [] and p.contraction_indices == ["i"]
+    p = ParsedEinsum.parse("i,j->ij", [(3,), (4,)])
+    assert p.contraction_indices == [] and p.compute_output_shape() == [3, 4]
+    p = ParsedEinsum.parse("bij,bjk->bik", [(2, 3, 4), (2, 4, 5)])
+    assert p.contraction_indices == ["j"] and p.compute_output_shape() == [2, 3, 5]
+    p = ParsedEinsum.parse("ij,jk", [(2, 3), (3, 4)])   # implicit output: indices that occur once
+    assert p.output_subscripts == ["i", "k"]
+    with pytest.raises(ValueError):
+        ParsedEinsum.parse("ij,jk->ik", [(2, 3), (4, 5)])
+    with pytest.raises(ValueError):
+        ParsedEinsum.parse("ij,jk->ik", [(2, 3)])
+    with pytest.raises(ValueError):
+        ParsedEinsum.parse("ij->iz", [(2, 3)])
+    # wire format of "ij,jk->ik" as the reference's test helper builds it
+    # (crates/hodu_cpu_kernels/tests/ops_einsum.rs:18-84)
+    p = ParsedEinsum.parse("ij,jk->ik", [(2, 3), (3, 4)])
+    md = einsum_metadata(p, [Layout.from_shape((2, 3)), Layout.from_shape((3, 4))], Layout.from_shape((2, 4)))
+    assert md == [8, 2, 3, 1, 2, 2, 4,  2, 2, 3, 3, 1, 0, 0, 1,  2, 3, 4, 4, 1, 0, 1, 2,  1,  2, 3, 4,  0, 2]
+
+
+def _einsum_md(eq, shapes):
+    from hodu_b200.einsum import ParsedEinsum, einsum_metadata
+    p = ParsedEinsum.parse(eq, shapes)
+    return einsum_metadata(p, [Layout.from_shape(s) for s in shapes],
+                           Layout.from_shape(tuple(p.compute_output_shape())))
+
+
+@pytest.mark.parametrize("eq,shapes", [("ii->", [(3, 3)]), ("ij->ji", [(2, 3)]), ("ij,jk->", [(2, 3), (3, 4)]),
+                                        ("ij,jk,kl->il", [(2, 3), (3, 4), (4, 5)]), ("bij,bjk->ibk", [(2, 3, 4), (2, 4, 5)]),
+                                        ("ii,ij->j", [(3, 3), (3, 2)])])
+def test_einsum_forms_that_are_not_matrix_products_are_refused(built_lib, eq, shapes):
+    md = _einsum_md(eq, shapes)
+    with pytest.raises(CudaKernelError) as e:   # refused while parsing: no device is touched
+        kernels.call_ops_einsum(kernels.einsum.F32, 0, [0x1000] * len(shapes), 0x2000, md)
+    assert e.value.code == -1
+
+
+def test_einsum_and_linear_argument_errors(built_lib):
+    md = _einsum_md("ij,jk->ik", [(2, 3), (3, 4)])
+    with pytest.raises(CudaKernelError) as e:
+        kernels.call_ops_einsum(kernels.einsum.F32, 0, [0x1000, 0x1000], 0x2000, md[:-1])
+    assert e.value.code == -2
+    with pytest.raises(CudaKernelError) as e:
+        kernels.call_ops_einsum(kernels.einsum.F64, 0, [0x1000, 0x1000], 0x2000, md)
+    assert e.value.code == -1
+    mm = matmul_metadata(Layout.from_shape((4, 8)), Layout.from_shape((8, 2)), Layout.from_shape((4, 2)))
+    with pytest.raises(CudaKernelError) as e:
+        kernels.call_ops_linear(DType.BF16, 0, 0x1000, 0x1000, 0x1000, 0x2000, [*mm, 1, 0], flags=7)
+    assert e.value.code == -2
+    with pytest.raises(CudaKernelError) as e:
+        kernels.call_ops_linear(DType.I8, 0, 0x1000, 0x1000, 0x1000, 0x2000, [*mm, 1, 0])
+    assert e.value.code == -1

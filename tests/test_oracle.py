@@ -197,3 +197,77 @@ def test_reference_per_dtype_kernels_are_not_the_oracle():
     O.ref().call("hodu_cpu_dot_bf16", ab, bb, ref_out, md)
     want = O.widen(O.matmul(ab, bb, md, O.BF16, is_dot=True), O.BF16)
     assert O.rel_err(O.bf16_to_f32(ref_out), want) > 1e-2
+
+
+# ---------------------------------------------------------------- einsum and Linear-with-bias
+from hodu_b200.einsum import ParsedEinsum, einsum_metadata  # noqa: E402
+
+GOLDEN_EL = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_einsum_linear.npz"))
+
+# The reference's own einsum known answers that are matrix products
+# (crates/hodu_cpu_kernels/tests/ops_einsum.rs:87-143,233-280,282-326,330-395).
+EINSUM_KNOWN = [
+    ("ij,jk->ik", [(2, 3), (3, 4)], [1, 2, 3, 4, 5, 6], list(range(1, 13)), [38, 44, 50, 56, 83, 98, 113, 128]),
+    ("i,j->ij", [(3,), (2,)], [1, 2, 3], [4, 5], [4, 5, 8, 10, 12, 15]),
+    ("i,i->", [(3,), (3,)], [1, 2, 3], [4, 5, 6], [32]),
+    ("bij,bjk->bik", [(2, 2, 3), (2, 3, 2)], list(range(1, 13)), list(range(1, 13)),
+     [22, 28, 49, 64, 220, 244, 301, 334]),
+]
+
+
+@pytest.mark.parametrize("case", EINSUM_KNOWN, ids=[c[0] for c in EINSUM_KNOWN])
+def test_reference_einsum_known_answers(case):
+    eq, shapes, a, b, want = case
+    parsed = ParsedEinsum.parse(eq, shapes)
+    md = einsum_metadata(parsed, [Layout.from_shape(s) for s in shapes],
+                         Layout.from_shape(tuple(parsed.compute_output_shape())))
+    got = O.einsum([np.array(a, dtype=np.float32), np.array(b, dtype=np.float32)], md, O.F32)
+    assert np.array_equal(got, np.array(want, dtype=np.float32))
+
+
+EINSUM_GOLDEN = sorted({k.split("__")[0] for k in GOLDEN_EL.files if k.startswith("einsum_")})
+
+
+@pytest.mark.parametrize("key", EINSUM_GOLDEN)
+def test_golden_einsum(key):
+    md = [int(v) for v in GOLDEN_EL[key + "__md"]]
+    ins = [GOLDEN_EL[key + "__in0"], GOLDEN_EL[key + "__in1"]]
+    want = GOLDEN_EL[key + "__out"]
+    if key.endswith("_i32"):
+        assert np.array_equal(O.einsum(ins, md, O.I32), want)
+    else:
+        # same sum, numpy's order of additions instead of the reference's k-order
+        assert O.rel_err(O.einsum(ins, md, O.F32), want) <= 2e-6
+
+
+def test_golden_linear_f32():
+    x, w, bias = GOLDEN_EL["linear_f32__x"], GOLDEN_EL["linear_f32__w"], GOLDEN_EL["linear_f32__bias"]
+    for each in (True, False):  # f32 storage: both rounding forms are the same arithmetic
+        got = O.linear(x, w.T, bias, O.F32, round_each_op=each)
+        assert O.rel_err(got, GOLDEN_EL["linear_f32__out"]) <= 2e-6
+
+
+def test_linear_rounding_forms_differ_for_bf16():
+    rng = np.random.default_rng(5)
+    x = O.widen(O.narrow(rng.standard_normal((8, 64)).astype(np.float32), O.BF16), O.BF16)
+    w = O.widen(O.narrow(rng.standard_normal((64, 16)).astype(np.float32), O.BF16), O.BF16)
+    b = O.widen(O.narrow(rng.standard_normal(16).astype(np.float32), O.BF16), O.BF16)
+    each, once = O.linear(x, w, b, O.BF16, True), O.linear(x, w, b, O.BF16, False)
+    assert O.rel_err(O.widen(each, O.BF16), O.widen(once, O.BF16)) <= 1e-2
+    assert not np.array_equal(each, once)  # two roundings vs one
+
+
+def test_einsum_against_compiled_reference_random():
+    ref = O.ref()
+    if ref is None or not hasattr(ref.base, "hodu_cpu_einsum_f32"):
+        pytest.skip("oracle/_ref not built (reference tree not mounted)")
+    rng = np.random.default_rng(11)
+    for eq, shapes in [("ij,jk->ik", [(9, 14), (14, 5)]), ("bhqd,bhkd->bhqk", [(2, 2, 3, 4), (2, 2, 5, 4)]),
+                       ("ik,jk->ji", [(6, 7), (4, 7)])]:
+        parsed = ParsedEinsum.parse(eq, shapes)
+        ol = Layout.from_shape(tuple(parsed.compute_output_shape()))
+        md = einsum_metadata(parsed, [Layout.from_shape(s) for s in shapes], ol)
+        ins = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+        want = np.zeros(ol.size(), dtype=np.float32)
+        ref.einsum("hodu_cpu_einsum_f32", ins, want, md)
+        assert O.rel_err(O.einsum(ins, md, O.F32), want) <= 2e-6
