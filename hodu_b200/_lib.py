@@ -26,6 +26,7 @@ SIGNATURES = {
     "hodu_b200_swiglu": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
     "hodu_b200_linear": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
     "hodu_b200_einsum": (_i, [_i, _vp, _u8, C.POINTER(C.c_void_p), _sz, _vp, _szp, _sz]),
+    "hodu_b200_conv2d": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _szp, _sz]),
     "hodu_b200_matmul_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_f32_static": (_i, [_i, _vp, _vp, _vp, _vp, _szp, _sz]),

@@ -88,6 +88,7 @@ DeviceState* device_state(int device) {
   st->cc_major = prop.major;
   st->cc_minor = prop.minor;
   st->smem_optin = prop.sharedMemPerBlockOptin;
+  st->device = device;
   if (cudaMalloc(&st->status, sizeof(uint32_t)) != cudaSuccess ||
       cudaMemset(st->status, 0, sizeof(uint32_t)) != cudaSuccess) {
     fail(HODU_B200_ERR_MEMORY, "cannot allocate the device status word on device %d", device);
@@ -96,6 +97,32 @@ DeviceState* device_state(int device) {
   }
   st->ready = true;
   return st;
+}
+
+int scratch_alloc(DeviceState* st, void** ptr, size_t bytes, cudaStream_t stream) {
+  if (!st->pool) {
+    std::lock_guard<std::mutex> lock(g_state_mu);
+    if (!st->pool) {
+      cudaMemPoolProps props = {};
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = st->device;
+      cudaMemPool_t pool = nullptr;
+      HODU_CUDA_TRY(cudaMemPoolCreate(&pool, &props), HODU_B200_ERR_MEMORY);
+      unsigned long long keep = ~0ull;  // never trim at synchronisation points
+      HODU_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep), HODU_B200_ERR_MEMORY);
+      st->pool = pool;
+    }
+  }
+  HODU_CUDA_TRY(cudaMallocFromPoolAsync(ptr, bytes, st->pool, stream), HODU_B200_ERR_MEMORY);
+  return 0;
+}
+
+int scratch_free(void* ptr, cudaStream_t stream) {
+  const cudaError_t e = cudaFreeAsync(ptr, stream);
+  if (e != cudaSuccess) return fail(HODU_B200_ERR_MEMORY, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
+  return 0;
 }
 
 // ------------------------------------------------------------------ metadata
@@ -276,6 +303,7 @@ void hodu_b200_shutdown(int device) {
     cudaDeviceSynchronize();
     release_host_pipeline(device);
     cudaFree(st->status);
+    if (st->pool) cudaMemPoolDestroy(st->pool);
   }
   *st = DeviceState();
 }
@@ -384,6 +412,32 @@ int hodu_b200_einsum(int device, void* stream, uint8_t dtype, const void* const*
   pb.b.ptr = inputs[swapped ? 0 : 1];
   pb.out = out;
   return run_problem(pb, st, static_cast<cudaStream_t>(stream));
+}
+
+int hodu_b200_conv2d(int device, void* stream, uint8_t dtype, const void* input, const void* weight,
+                     void* out, const size_t* md, size_t len) {
+  if (dtype != HODU_DTYPE_BF16 && dtype != HODU_DTYPE_F16 && dtype != HODU_DTYPE_F32)
+    return fail(HODU_B200_ERR_INVALID_KERNEL, "conv2d: unsupported dtype %s", dtype_name(dtype));
+  if (!md || len != 18) return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: metadata length %zu, expected 18", len);
+  const size_t B = md[1], cin = md[2], cout = md[3], H = md[4], W = md[5], KH = md[6], KW = md[7];
+  const size_t OH = md[8], OW = md[9], sh = md[10], sw = md[11], ph = md[12], pw = md[13], dh = md[14], dw = md[15];
+  if (sh == 0 || sw == 0 || dh == 0 || dw == 0 || KH == 0 || KW == 0)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: zero stride, dilation or kernel extent");
+  const size_t span_h = dh * (KH - 1) + 1, span_w = dw * (KW - 1) + 1;
+  if (H + 2 * ph < span_h || W + 2 * pw < span_w)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: kernel larger than the padded input");
+  if (OH != (H + 2 * ph - span_h) / sh + 1 || OW != (W + 2 * pw - span_w) / sw + 1)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: output extent %zux%zu disagrees with input, kernel, stride, padding and dilation", OH, OW);
+  if (md[0] != B * cout * OH * OW)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: num_els %zu != batch*out_channels*out_h*out_w", md[0]);
+  if (md[0] == 0) return 0;
+  if (cin == 0) return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: in_channels == 0");
+  if (!input || !weight || !out) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+  return run_conv2d(dtype, input, weight, out, md, len, st, static_cast<cudaStream_t>(stream));
 }
 
 const char* hodu_b200_strerror(int code) {

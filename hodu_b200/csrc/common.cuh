@@ -44,7 +44,14 @@ struct DeviceState {
   int cc_major = 0, cc_minor = 0;
   size_t smem_optin = 0;
   uint32_t* status = nullptr;  // one device word: first bounded wait that gave up
+  int device = -1;
+  cudaMemPool_t pool = nullptr;  // scratch pool of this library (created on first use)
 };
+// Stream-ordered scratch from a memory pool that belongs to this library (the caller's default
+// pool is left alone).  The pool keeps what it has handed out for reuse until
+// hodu_b200_shutdown, so repeated calls do not go back to the driver for memory.
+int scratch_alloc(DeviceState* st, void** ptr, size_t bytes, cudaStream_t stream);
+int scratch_free(void* ptr, cudaStream_t stream);
 // Returns the state for `device`, initialising it on first use (thread-safe);
 // nullptr + recorded error on failure.
 DeviceState* device_state(int device);
@@ -117,6 +124,9 @@ int parse_einsum(const size_t* md, size_t len, size_t num_inputs, Problem* pb, b
 int check_operands(int in_dtype, int out_dtype, const void* lhs, const void* rhs, void* out,
                    float scale_lhs, float scale_rhs, uint32_t epilogue);
 int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream);
+// conv2d wire format (validated by the caller) -> im2col + one batched product (conv.cu).
+int run_conv2d(int dtype, const void* input, const void* weight, void* out, const size_t* md, size_t len,
+               DeviceState* st, cudaStream_t stream);
 // Frees the staging memory and streams of the host-buffer forms (host_pipeline.cu).
 void release_host_pipeline(int device);
 // Casts.

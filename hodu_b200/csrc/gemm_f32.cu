@@ -179,11 +179,10 @@ int launch_gemm_f32(const Problem& pb, DeviceState* st, cudaStream_t stream, con
   const size_t bytes = gemm_f32_scratch_bytes(pb);
   if (bytes == 0) { *why = "more than three batch dims"; return 1; }
   void* scratch = nullptr;
-  HODU_CUDA_TRY(cudaMallocAsync(&scratch, bytes, stream), HODU_B200_ERR_MEMORY);
+  if (const int ra = scratch_alloc(st, &scratch, bytes, stream)) return ra;
   const int r = launch_gemm_f32_split(pb, st, stream, scratch, bytes, why);
-  const cudaError_t e = cudaFreeAsync(scratch, stream);
-  if (r == 0 && e != cudaSuccess) return fail(HODU_B200_ERR_MEMORY, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
-  return r;
+  const int rf = scratch_free(scratch, stream);
+  return r ? r : rf;
 }
 
 }  // namespace hodu_b200

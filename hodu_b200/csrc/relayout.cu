@@ -131,7 +131,7 @@ int launch_gemm_tc_relayout(const Problem& pb, DeviceState* st, cudaStream_t str
   if (need_b) { if (!plan_copy(pb, pb.b, false, esize, &pbp)) return 1; total += pbp.bytes; }
   if (need_b2) { if (!plan_copy(pb, pb.b2, false, esize, &pb2)) return 1; total += pb2.bytes; }
   uint8_t* scratch = nullptr;
-  HODU_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&scratch), total, stream), HODU_B200_ERR_MEMORY);
+  if (const int ra = scratch_alloc(st, reinterpret_cast<void**>(&scratch), total, stream)) return ra;
   Problem q = pb;
   uint8_t* cur = scratch;
   int r = 0;
@@ -139,9 +139,8 @@ int launch_gemm_tc_relayout(const Problem& pb, DeviceState* st, cudaStream_t str
   if (!r && need_b) { r = run_copy(pbp, pb.b, esize, cur, st, stream); q.b = pbp.out; q.b.ptr = cur; cur += pbp.bytes; }
   if (!r && need_b2) { r = run_copy(pb2, pb.b2, esize, cur, st, stream); q.b2 = pb2.out; q.b2.ptr = cur; cur += pb2.bytes; }
   if (!r) r = launch_gemm_tc(q, st, stream, why);
-  const cudaError_t e = cudaFreeAsync(scratch, stream);
-  if (r == 0 && e != cudaSuccess) return fail(HODU_B200_ERR_MEMORY, "cudaFreeAsync failed: %s", cudaGetErrorString(e));
-  return r;
+  const int rf = scratch_free(scratch, stream);
+  return r ? r : rf;
 }
 
 }  // namespace hodu_b200

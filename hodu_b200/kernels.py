@@ -44,6 +44,7 @@ matmul = _Family("matmul")
 dot = _Family("dot")
 cast = _Family("cast")
 einsum = _Family("einsum")
+conv2d = _Family("conv2d")
 
 
 def _parse(kernel: Kernel, op: str):
@@ -122,6 +123,14 @@ def call_ops_einsum(kernel: Kernel, device: int, inputs: Sequence[int], output: 
     md = metadata_array(metadata)
     ptrs = (C.c_void_p * len(inputs))(*[int(p) for p in inputs])
     check(_lib.lib().hodu_b200_einsum(device, stream, int(dt), ptrs, len(inputs), output, md, len(metadata)))
+
+
+def call_ops_conv(kernel: Kernel, device: int, input: int, weight: int, output: int,
+                  metadata: Sequence[int], stream: int = 0) -> None:
+    """`call_ops_conv` (crates/hodu_cuda_kernels/src/kernels/ops_conv.rs) for conv2d."""
+    dt = _parse(kernel, "conv2d")
+    md = metadata_array(metadata)
+    check(_lib.lib().hodu_b200_conv2d(device, stream, int(dt), input, weight, output, md, len(metadata)))
 
 
 def call_ops_matmul_host(in_dtype: DType, out_dtype: DType, device: int, lhs_host: int, rhs_host: int,

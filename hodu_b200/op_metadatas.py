@@ -61,3 +61,17 @@ def swiglu_metadata(x: Layout, w_gate: Layout, w_up: Layout) -> List[int]:
     n = w_gate.shape[1]
     return [m, k, n, x.strides[0], x.strides[1], w_gate.strides[0], w_gate.strides[1],
             w_up.strides[0], w_up.strides[1], x.offset, w_gate.offset, w_up.offset]
+
+
+def conv2d_metadata(batch: int, in_channels: int, out_channels: int, in_hw, kernel_hw, stride=(1, 1),
+                    padding=(0, 0), dilation=(1, 1), input_offset: int = 0, weight_offset: int = 0) -> List[int]:
+    """[num_els, batch, in_channels, out_channels, in_h, in_w, kernel_h, kernel_w, out_h, out_w,
+    stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, input_offset, weight_offset]
+    (op_metadatas.rs:1076-1123); the output extents follow from the others."""
+    (h, w), (kh, kw), (sh, sw), (ph, pw), (dh, dw) = in_hw, kernel_hw, stride, padding, dilation
+    oh = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+    ow = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+    if oh <= 0 or ow <= 0:
+        raise ValueError("conv2d: kernel larger than the padded input")
+    return [batch * out_channels * oh * ow, batch, in_channels, out_channels, h, w, kh, kw, oh, ow,
+            sh, sw, ph, pw, dh, dw, input_offset, weight_offset]

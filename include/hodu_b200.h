@@ -230,6 +230,23 @@ int hodu_b200_einsum(int device, void* stream, uint8_t dtype, const void* const*
                      size_t num_inputs, void* out, const size_t* metadata, size_t metadata_len);
 
 /*
+ * conv2d (NCHW input, [Cout,Cin,KH,KW] weight, NCHW output) as im2col + one batched product on
+ * the same GEMM kernels.  Replaces `call_ops_conv` with `hodu_cuda_conv2d_{dtype}`
+ * (crates/hodu_cuda_kernels/src/kernels/ops_conv.rs; direct kernel
+ * crates/hodu_cuda_kernels/kernels/ops_conv.cu:45-93), in the form the reference's CPU OpenBLAS
+ * build uses (crates/hodu_cpu_kernels/kernels/ops_conv_openblas.c:84-133).
+ * metadata = `conv2d_metadata` (crates/hodu_core/src/op_metadatas.rs:1076-1123), 18 words:
+ *   [num_els, batch, in_channels, out_channels, in_h, in_w, kernel_h, kernel_w, out_h, out_w,
+ *    stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, input_offset, weight_offset]
+ * Input and weight are contiguous from their offsets.  dtype: bf16 | f16 | f32; f32 accumulate,
+ * one rounding.  The unfolded input lives in stream-ordered scratch for the duration of the call
+ * (at most 2 GiB at a time; larger batches run in several passes); a 1x1 kernel with unit stride
+ * and no padding needs none.
+ */
+int hodu_b200_conv2d(int device, void* stream, uint8_t dtype, const void* input, const void* weight,
+                     void* out, const size_t* metadata, size_t metadata_len);
+
+/*
  * Host-buffer forms: the whole of "create tensors on the device, multiply, read
  * the result back", i.e. `BackendDevice` upload (crates/hodu_core/src/be/device.rs:35-55),
  * `call_ops_matmul` / `call_ops_dot`, then `to_cpu_storage`

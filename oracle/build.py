@@ -3,7 +3,7 @@
   oracle/_build/liboracle.so        the C restatement in hodu_oracle.c (gcc)
   oracle/_ref/libhodu_ref.so        the REFERENCE's own C kernels for this path, compiled
                                     from the sources where they lie (never copied here):
-                                    ops_matrix.c, ops_cast.c, ops_unary.c, ops_binary.c, ops_einsum.c
+                                    ops_matrix.c, ops_cast.c, ops_unary.c, ops_binary.c, ops_einsum.c, ops_conv.c
   oracle/_ref/libhodu_ref_blas.so   the reference's OpenBLAS variant ops_matrix_openblas.c
                                     (hodu_cpu_matmul_f32 / hodu_cpu_dot_f32 = cblas_sgemm),
                                     linked against an OpenBLAS found in site-packages
@@ -76,8 +76,8 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT):
     flags = ["-std=c11", "-O3", "-march=x86-64-v3", "-DENABLE_THREADS", "-fPIC", "-shared", "-I", kdir]
     out = os.path.join(REF, "libhodu_ref.so")
     srcs = [os.path.join(kdir, f) for f in ("ops_matrix.c", "ops_cast.c", "ops_unary.c", "ops_binary.c",
-                                            "ops_einsum.c")]
-    if os.path.exists(out) and not _exports(out, "hodu_cpu_einsum_f32"):
+                                            "ops_einsum.c", "ops_conv.c")]
+    if os.path.exists(out) and not _exports(out, "hodu_cpu_conv2d_f32_fallback"):
         os.remove(out)  # built from an earlier, shorter source list
     if not os.path.exists(out):
         _run(["gcc", *flags, *srcs, "-o", out, "-lpthread", "-lm"])

@@ -385,6 +385,27 @@ def einsum(inputs: Sequence[np.ndarray], md: Sequence[int], dtype: int) -> np.nd
     return narrow(np.asarray(c, dtype=np.float32), dtype).reshape(-1)
 
 
+def conv2d(inp: np.ndarray, weight: np.ndarray, md: Sequence[int], dtype: int) -> np.ndarray:
+    """Oracle of conv2d for storage dtype `dtype`: NCHW input and [Cout,Cin,KH,KW] weight,
+    contiguous from their offsets; every output element is the f32 sum over (ic, kh, kw) of
+    input x weight with zero padding, converted once
+    (crates/hodu_cuda_kernels/kernels/ops_conv.cu:65-92; the CPU f32 form
+    crates/hodu_cpu_kernels/kernels/ops_conv.c:172-232 is the same sum).  Computed as
+    unfold + f32 matrix product per image.  Returns raw storage, flat [B, Cout, OH, OW]."""
+    (_n, B, cin, cout, H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw, ioff, woff) = [int(v) for v in md]
+    x = widen(inp.reshape(-1)[ioff:ioff + B * cin * H * W], dtype).reshape(B, cin, H, W)
+    w = widen(weight.reshape(-1)[woff:woff + cout * cin * KH * KW], dtype).reshape(cout, cin * KH * KW)
+    xp = np.zeros((B, cin, H + 2 * ph, W + 2 * pw), dtype=np.float32)
+    xp[:, :, ph:ph + H, pw:pw + W] = x
+    col = np.empty((B, cin, KH, KW, OH, OW), dtype=np.float32)
+    for kh in range(KH):
+        for kw in range(KW):
+            col[:, :, kh, kw] = xp[:, :, kh * dh:kh * dh + (OH - 1) * sh + 1:sh, kw * dw:kw * dw + (OW - 1) * sw + 1:sw]
+    col = col.reshape(B, cin * KH * KW, OH * OW)
+    out = np.matmul(w[None], col).astype(np.float32)
+    return narrow(out, dtype).reshape(-1)
+
+
 def rel_err(got_f32: np.ndarray, want_f32: np.ndarray) -> float:
     """max|got - want| / max|want| -- the error measure of the floating-point parity bars."""
     want = np.asarray(want_f32, dtype=np.float64)

@@ -271,3 +271,29 @@ def test_einsum_against_compiled_reference_random():
         want = np.zeros(ol.size(), dtype=np.float32)
         ref.einsum("hodu_cpu_einsum_f32", ins, want, md)
         assert O.rel_err(O.einsum(ins, md, O.F32), want) <= 2e-6
+
+
+# ---------------------------------------------------------------- conv2d
+from hodu_b200.op_metadatas import conv2d_metadata  # noqa: E402
+
+GOLDEN_CONV = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_conv2d.npz"))
+CONV_GOLDEN = sorted({k.split("__")[0] for k in GOLDEN_CONV.files})
+
+
+def test_reference_conv2d_known_answers():
+    # crates/hodu_cpu_kernels/tests/ops_conv.rs:95-147 and :150-202
+    x = np.arange(1, 10, dtype=np.float32)
+    md = conv2d_metadata(1, 1, 1, (3, 3), (2, 2))
+    assert md == [4, 1, 1, 1, 3, 3, 2, 2, 2, 2, 1, 1, 0, 0, 1, 1, 0, 0]
+    assert np.array_equal(O.conv2d(x, np.array([1, 0, 0, 1], dtype=np.float32), md, O.F32), [6, 8, 12, 14])
+    md = conv2d_metadata(1, 1, 1, (3, 3), (3, 3), padding=(1, 1))
+    assert md[8:10] == [3, 3]
+    w = np.array([0, 0, 0, 0, 1, 0, 0, 0, 0], dtype=np.float32)
+    assert np.array_equal(O.conv2d(x, w, md, O.F32), x)
+
+
+@pytest.mark.parametrize("name", CONV_GOLDEN)
+def test_golden_conv2d(name):
+    md = [int(v) for v in GOLDEN_CONV[name + "__md"]]
+    got = O.conv2d(GOLDEN_CONV[name + "__in"], GOLDEN_CONV[name + "__w"], md, O.F32)
+    assert O.rel_err(got, GOLDEN_CONV[name + "__out"]) <= 2e-6
