@@ -349,6 +349,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU runs the whole configuration; strong: the one configuration is sharded over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="after the timed region: per-step best/median and a back-to-back run of this length (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -411,6 +413,33 @@ def main():
     is_cast = args.workload in CAST_WORKLOADS
     per_unit = 1e9 if is_cast else 1e12   # casts count bytes (GB/s), products count flops (TFLOP/s)
     value = total_flops / (ms_per_step * 1e-3) / per_unit
+
+    # ---- spread and a sustained figure (1 GPU only; outside the timed region above) -------------
+    detail = None
+    if world == 1 and args.sustained_seconds > 0:
+        n_d = max(5, min(args.steps, 100))
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_d + 1)]
+        evs[0].record(stream)
+        for i in range(n_d):
+            wl.step()
+            evs[i + 1].record(stream)
+        torch.cuda.synchronize(dev)
+        per = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(n_d))
+        to_rate = lambda ms: wl.flops / (ms * 1e-3) / per_unit
+        n_s = int(min(200000, max(args.steps, args.sustained_seconds * 1e3 / max(ms_per_step, 1e-3))))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(uuid) as sclocks:
+            s0.record(stream)
+            for _ in range(n_s):
+                wl.step()
+            s1.record(stream)
+            torch.cuda.synchronize(dev)
+        s_ms = s0.elapsed_time(s1)
+        detail = {"per_step": {"steps": n_d, "best": to_rate(per[0]), "median": to_rate(per[n_d // 2]),
+                               "note": "one CUDA event per step; includes the gap to the previous launch"},
+                  "sustained": {"value": to_rate(s_ms / n_s), "seconds": s_ms * 1e-3, "steps": n_s,
+                                "clocks": sclocks.summary()}}
+        K.last_status(local)
 
     # ---- e2e through the host-buffer entry point ------------------------------------------------
     e2e = None
@@ -477,6 +506,8 @@ def main():
         line["roofline"]["frac_of_nominal"] = achieved / NOMINAL_PEAK_TFLOPS[args.workload]
     if e2e is not None:
         line["e2e"] = e2e
+    if detail is not None:
+        line["spread"] = detail
     if world == 1 and not args.no_cpu_baseline:
         v, kind, cores, sample, secs = (cpu_reference_cast_rate if is_cast else cpu_reference_rate)(args.workload, 15.0)
         line["cpu_baseline"] = {"value": v, "unit": "GB/s" if is_cast else "TFLOP/s", "cores": cores, "kind": kind,

@@ -58,7 +58,10 @@ int forced_path() {
 
 DeviceGuard::DeviceGuard(int device) {
   if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; }
-  ok = (prev == device) || cudaSetDevice(device) == cudaSuccess;
+  // Always set the device, also when it already is the current one: on a thread that has made
+  // no CUDA call yet this is what binds the device's primary context to the thread, and the
+  // driver entry points used afterwards (tensor-map encoding) need a current context.
+  ok = cudaSetDevice(device) == cudaSuccess;
   if (prev == device) prev = -1;  // nothing to restore
 }
 DeviceGuard::~DeviceGuard() {

@@ -911,7 +911,10 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   const CUresult r = enc(&out->map, dt, 5, reinterpret_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled rejected the layout";
+  if (r == CUDA_ERROR_INVALID_VALUE) return "cuTensorMapEncodeTiled rejected the layout";
+  // Anything else (no current context, driver shut down) is a failure of the call, not a
+  // property of the layout: the leading '!' makes the caller report it instead of falling back.
+  if (r != CUDA_SUCCESS) return "!cuTensorMapEncodeTiled failed (no usable CUDA context on this thread?)";
   return nullptr;
 }
 
@@ -1080,14 +1083,15 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   const uint32_t a_rows_staged = static_cast<uint32_t>(BM * mh);
   const char* err = build_operand_map(pb.a, esize, pb.M, pb.K, /*k_is_col=*/true, bd, bd.a_stride, a_rows_staged,
                                       a_rows_staged / mn_per_slab, &oa);
-  if (err) { *why = err; return 1; }
+  auto refuse = [&](const char* e) { *why = e; return e[0] == '!' ? fail(HODU_B200_ERR_LAUNCH, "%s", e + 1) : 1; };
+  if (err) return refuse(err);
   err = build_operand_map(pb.b, esize, pb.K, pb.N, /*k_is_col=*/false, bd, bd.b_stride, b_cols_per_box,
                           b_cols_per_box / mn_per_slab, &ob);
-  if (err) { *why = err; return 1; }
+  if (err) return refuse(err);
   if (pb.swiglu) {
     err = build_operand_map(pb.b2, esize, pb.K, pb.N, false, bd, bd.b2_stride, b_cols_per_box,
                             b_cols_per_box / mn_per_slab, &ob2);
-    if (err) { *why = err; return 1; }
+    if (err) return refuse(err);
     if (ob2.mn_major != ob.mn_major || ob2.slab_dim != ob.slab_dim) { *why = "gate and up weights differ in layout"; return 1; }
     for (int j = 0; j < 3; ++j)
       if (ob2.bmul[j] != ob.bmul[j]) { *why = "gate and up weights differ in batch broadcast"; return 1; }

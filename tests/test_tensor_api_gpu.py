@@ -152,3 +152,60 @@ def test_bounded_wait_reports_through_the_status_word():
         K.force_path(_lib.PATH_AUTO)
     assert K.last_status(0) == 0
     assert np.all(O.widen(from_dev(out, O.BF16), O.BF16) == 64.0)
+
+
+def test_concurrent_calls_from_several_threads_on_one_device():
+    """`call_ops_matmul` may be called from any thread, two threads at once on the same device
+    (the reference's `Kernels` / device pool are RwLock-guarded maps: src/kernel.rs:102-107).
+    Four threads, each on its own stream, alternate two shapes so that tensor-map encoding, the
+    per-instantiation launch set-up and the scratch pool are all hit concurrently."""
+    import threading
+    import torch
+    from hodu_b200 import kernels as K
+    from hodu_b200.layout import Layout
+    from hodu_b200.op_metadatas import dot_metadata
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(1)
+    shapes = [(512, 384, 256, torch.bfloat16, K.dot.BF16), (256, 512, 384, torch.float32, K.dot.F32)]
+    data = []
+    for m, k, n, dt, kern in shapes:
+        a = torch.randn(m, k, generator=g, device=dev).to(dt)
+        b = torch.randn(k, n, generator=g, device=dev).to(dt)
+        out = torch.empty(m * n, dtype=dt, device=dev)
+        K.call_ops_dot(kern, 0, a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                       dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n))), 0)
+        torch.cuda.synchronize()
+        data.append((a, b, out.clone()))
+    errors = []
+
+    def worker(tid):
+        try:
+            s = torch.cuda.Stream(device=dev)
+            for it in range(40):
+                m, k, n, dt, kern = shapes[(tid + it) % 2]
+                a, b, want = data[(tid + it) % 2]
+                out = torch.empty(m * n, dtype=dt, device=dev)
+                K.call_ops_dot(kern, 0, a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                               dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n))), s.cuda_stream)
+                if K.last_path() != _lib.PATH_TENSOR:   # a fresh thread must not fall back silently
+                    errors.append(f"thread {tid} iteration {it}: path {K.last_path()} instead of the tensor-core kernel")
+                    return
+                s.synchronize()
+                if not torch.equal(out, want):
+                    d = (out != want).reshape(m, n)
+                    rows, cols = d.any(1).nonzero().flatten().tolist(), d.any(0).nonzero().flatten().tolist()
+                    errors.append(f"thread {tid} iteration {it} ({m}x{k}x{n}): {int(d.sum())} elements differ from the "
+                                  f"single-threaded result; rows {rows[:2]}..{rows[-2:]} ({len(rows)}), "
+                                  f"cols {cols[:2]}..{cols[-2:]} ({len(cols)}), "
+                                  f"max |diff| {(out.float() - want.float()).abs().max().item():.3g}")
+                    return
+        except Exception as e:  # noqa: BLE001
+            errors.append(f"thread {tid}: {e!r}")
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert K.last_status(0) == 0
