@@ -86,7 +86,8 @@ struct Problem {
   Operand b2;            // second right-hand operand (SwiGLU up projection)
   bool swiglu = false;
   uint32_t swiglu_flags = 0;
-  void* out = nullptr;   // contiguous [batches, M, N]
+  void* out = nullptr;   // [batches, M, N]; rows `ldc` elements apart, batches M*ldc apart
+  int64_t ldc = 0;       // 0: N (a contiguous output, what every entry point of the C ABI passes)
   float alpha = 1.0f;    // scale_lhs * scale_rhs
   // Bias of a Linear layer: [N] values of the OUTPUT dtype added to every output row
   // (hodu_nn/src/modules/linear.rs:38-47).  `bias_flags` says whether the product is rounded

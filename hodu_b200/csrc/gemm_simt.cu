@@ -34,7 +34,7 @@ struct SimtParams {
   long long a_bs[16], b_bs[16], b2_bs[16];
   float alpha;
   unsigned swiglu_flags;
-  long long tiles_m, tiles_n;
+  long long tiles_m, tiles_n, ldc;
   const void* bias;        // [N] of TOut (offset applied), or null
   long long bias_stride;
   unsigned bias_flags;
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
       __syncthreads();
     }
 
-    TOut* O = static_cast<TOut*>(p.out) + batch * p.M * p.N;
+    TOut* O = static_cast<TOut*>(p.out) + batch * p.M * p.ldc;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const long long gi = m0 + ty * 4 + i;
@@ -160,16 +160,16 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
           } else {
             v = silu_ref(g) * u;
           }
-          O[gi * p.N + gj] = Narrow<TOut, float>::put(v);
+          O[gi * p.ldc + gj] = Narrow<TOut, float>::put(v);
         } else if constexpr (std::is_same<Acc, float>::value) {
           float v = acc[i][j] * p.alpha;
           if (p.bias) {
             if (p.bias_flags == HODU_B200_LINEAR_ROUND_EACH_OP) v = Widen<TOut>::get(Narrow<TOut, float>::put(v));
             v += Widen<TOut>::get(static_cast<const TOut*>(p.bias)[gj * p.bias_stride]);
           }
-          O[gi * p.N + gj] = Narrow<TOut, Acc>::put(v);
+          O[gi * p.ldc + gj] = Narrow<TOut, Acc>::put(v);
         } else {
-          O[gi * p.N + gj] = Narrow<TOut, Acc>::put(acc[i][j]);
+          O[gi * p.ldc + gj] = Narrow<TOut, Acc>::put(acc[i][j]);
         }
       }
     }
@@ -211,6 +211,7 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   p.bias = pb.bias ? static_cast<const uint8_t*>(pb.bias) + pb.bias_offset * dtype_size(pb.out_dtype) : nullptr;
   p.bias_stride = pb.bias_stride;
   p.bias_flags = pb.bias_flags;
+  p.ldc = pb.ldc > 0 ? pb.ldc : pb.N;
   p.tiles_m = (pb.M + TM - 1) / TM;
   p.tiles_n = (pb.N + TN - 1) / TN;
   const long long tiles = p.tiles_m * p.tiles_n * pb.batches;

@@ -1106,6 +1106,15 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   p.bk = 128u / esize;
   p.k_blocks = static_cast<uint32_t>((pb.K + p.bk - 1) / p.bk);
   p.group_m = form == 2 ? 4 : (form == 1 ? 8 : 16);  // 2048 rows of A per raster group
+  {
+    // HODU_B200_GROUP_ROWS=<rows of A per raster group> overrides the default (tuning aid).
+    static const int rows_override = [] { const char* e = getenv("HODU_B200_GROUP_ROWS"); return e ? atoi(e) : 0; }();
+    if (rows_override >= 128) {
+      const uint32_t tile_rows = form == 2 ? 512u : (form == 1 ? 256u : 128u);
+      p.group_m = static_cast<uint32_t>(rows_override) / tile_rows;
+      if (p.group_m < 1) p.group_m = 1;
+    }
+  }
   p.bdim1 = static_cast<uint32_t>(bd.size[1]); p.bdim2 = static_cast<uint32_t>(bd.size[2]);
 
   const uint32_t slab_bytes = 128u * p.bk;          // MN-major slab: bk rows of 128 bytes
@@ -1138,12 +1147,12 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   p.bias = pb.bias ? static_cast<const uint8_t*>(pb.bias) + pb.bias_offset * dtype_size(pb.out_dtype) : nullptr;
   p.bias_stride = pb.bias_stride;
   p.bias_flags = pb.bias_flags;
-  p.ldc = static_cast<unsigned long long>(pb.N);
-  p.out_batch_stride = static_cast<unsigned long long>(pb.M) * static_cast<unsigned long long>(pb.N);
+  p.ldc = static_cast<unsigned long long>(pb.ldc > 0 ? pb.ldc : pb.N);
+  p.out_batch_stride = static_cast<unsigned long long>(pb.M) * p.ldc;
   p.out = pb.out;
   p.status = st->status;
   const int osz = dtype_size(pb.out_dtype);
-  p.out_vec_ok = (reinterpret_cast<uintptr_t>(pb.out) % 16 == 0 && (pb.N * osz) % 16 == 0 &&
+  p.out_vec_ok = (reinterpret_cast<uintptr_t>(pb.out) % 16 == 0 && (p.ldc * osz) % 16 == 0 &&
                   (p.out_batch_stride * osz) % 16 == 0) ? 1u : 0u;
 #ifdef HODU_TC_PROFILE
   if (const char* e = getenv("HODU_TC_EXPERIMENT")) p.out_vec_ok |= static_cast<uint32_t>(atoi(e)) & 14u;

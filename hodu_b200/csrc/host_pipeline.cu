@@ -21,7 +21,8 @@ constexpr int kMaxSlices = 64;
 
 // Tuning knobs read once from the environment: HODU_B200_HOST_SLICES (slices per call, default
 // 8) and HODU_B200_HOST_LANES (1, the default: one stream per direction -- upload, compute,
-// download -- chained by events; 0: each slice's three steps on one of four rotating streams).
+// download -- chained by events; 0: each slice's three steps on one of four rotating streams),
+// HODU_B200_HOST_PANELS (column panels of a single large rhs, default 4; 1: upload it whole).
 // On a PCIe 5 x16 B200 the schedules differ by a few per cent only: the 16x2048^3 bf16 product
 // (256 MiB up, 128 MiB down) takes 5.8-6.1 ms under all of them, against 5.2 ms for the two bare
 // copies issued together.
@@ -32,6 +33,7 @@ int env_int(const char* name, int dflt, int lo, int hi) {
   return v < lo ? lo : (v > hi ? hi : v);
 }
 int host_slices() { static const int v = env_int("HODU_B200_HOST_SLICES", 8, 1, kMaxSlices); return v; }
+int host_panels() { static const int v = env_int("HODU_B200_HOST_PANELS", 4, 1, 8); return v; }
 bool host_lanes() { static const int v = env_int("HODU_B200_HOST_LANES", 1, 0, 1); return v != 0; }
 
 struct HostPipe {
@@ -153,6 +155,74 @@ int host_impl(bool is_dot, int device, int in_dtype, int out_dtype, const void* 
       if (r) return r;
       if (lanes) { r = hand_over(hp->computed[idx], s, hp->stream[2]); if (r) return r; s = hp->stream[2]; }
       HODU_CUDA_TRY(cudaMemcpyAsync(ho + co, dout + co, static_cast<size_t>(nb) * pb.M * pb.N * osz, cudaMemcpyDeviceToHost, s), HODU_B200_ERR_MEMORY);
+    }
+  } else if ((pb.batches == 1 || (!b_batched && a_batched)) && lanes && host_panels() > 1 &&
+             pb.N >= 512 * host_panels() && static_cast<size_t>(b_elems) * isz >= (size_t(8) << 20)) {
+    // One large rhs for every row of the (flattened) lhs.  Waiting for the whole rhs before the
+    // first product would delay the first download by its upload time, so the rhs travels in
+    // column panels as well: block (i, j) of the output needs row block i of the lhs and panel j
+    // of the rhs only.  Panels and output blocks are pitched (2-D) copies; the kernels write
+    // their block straight into the full-size output.
+    const int64_t rows = a_batched ? pb.batches * pb.M : pb.M;
+    const int panels = host_panels();
+    int64_t nbw = (pb.N + panels - 1) / panels;
+    nbw = (nbw + 255) / 256 * 256;
+    int row_blocks = kMaxSlices / panels < host_slices() ? kMaxSlices / panels : host_slices();
+    if (row_blocks > 4) row_blocks = 4;
+    int64_t per = (rows + row_blocks - 1) / row_blocks;
+    per = (per + 127) / 128 * 128;
+    cudaStream_t up = hp->stream[0], comp = hp->stream[1], down = hp->stream[2];
+    const int n_panels = static_cast<int>((pb.N + nbw - 1) / nbw), n_rows = static_cast<int>((rows + per - 1) / per);
+    if (n_panels * n_rows > kMaxSlices) return fail(HODU_B200_ERR_INVALID_INPUT, "host form: too many blocks");
+    auto upload_panel = [&](int j) -> int {
+      const int64_t c0 = j * nbw, nc = c0 + nbw <= pb.N ? nbw : pb.N - c0;
+      HODU_CUDA_TRY(cudaMemcpy2DAsync(dr + c0 * isz, pb.N * isz, hr + c0 * isz, pb.N * isz, nc * isz, pb.K,
+                                      cudaMemcpyHostToDevice, up), HODU_B200_ERR_MEMORY);
+      return 0;
+    };
+    auto upload_rows = [&](int i) -> int {
+      const int64_t r0 = i * per, nr = r0 + per <= rows ? per : rows - r0;
+      const size_t ao = static_cast<size_t>(r0) * pb.K * isz;
+      HODU_CUDA_TRY(cudaMemcpyAsync(dl + ao, hl + ao, static_cast<size_t>(nr) * pb.K * isz, cudaMemcpyHostToDevice, up), HODU_B200_ERR_MEMORY);
+      return 0;
+    };
+    int idx = 0;
+    auto block = [&](int i, int j) -> int {   // product and download of output block (i, j)
+      const int64_t r0 = i * per, nr = r0 + per <= rows ? per : rows - r0;
+      const int64_t c0 = j * nbw, nc = c0 + nbw <= pb.N ? nbw : pb.N - c0;
+      const size_t co = (static_cast<size_t>(r0) * pb.N + c0) * osz;
+      Problem q = pb;
+      q.batch_ndim = 0; q.batches = 1; q.M = nr; q.N = nc;
+      q.a.ptr = dl + static_cast<size_t>(r0) * pb.K * isz; q.a.stride_r = pb.K; q.a.stride_c = 1;
+      q.b.ptr = dr + c0 * isz; q.b.stride_r = pb.N; q.b.stride_c = 1;
+      q.out = dout + co; q.ldc = pb.N;
+      int rr = hand_over(hp->uploaded[idx], up, comp);
+      if (rr) return rr;
+      rr = run_problem(q, st, comp);
+      if (rr) return rr;
+      rr = hand_over(hp->computed[idx], comp, down);
+      if (rr) return rr;
+      ++idx;
+      HODU_CUDA_TRY(cudaMemcpy2DAsync(ho + co, pb.N * osz, dout + co, pb.N * osz, nc * osz, nr,
+                                      cudaMemcpyDeviceToHost, down), HODU_B200_ERR_MEMORY);
+      return 0;
+    };
+    // Uploads alternate between a panel and a row block, so the set of blocks that can be
+    // computed grows as a square (1, 2, 4, 6, 9, ..) and the download never waits long.
+    int have_rows = 0, have_panels = 0;
+    while (have_rows < n_rows || have_panels < n_panels) {
+      const bool take_panel = have_panels < n_panels && (have_panels <= have_rows || have_rows == n_rows);
+      if (take_panel) {
+        if ((r = upload_panel(have_panels))) return r;
+        for (int i = 0; i < have_rows; ++i)
+          if ((r = block(i, have_panels))) return r;
+        ++have_panels;
+      } else {
+        if ((r = upload_rows(have_rows))) return r;
+        for (int j = 0; j < have_panels; ++j)
+          if ((r = block(have_rows, j))) return r;
+        ++have_rows;
+      }
     }
   } else if (pb.batches == 1 || (!b_batched && a_batched)) {
     // One rhs for every row of the (flattened) lhs: upload it once, then stream

@@ -103,7 +103,11 @@ def test_host_buffer_forms_match_device_forms(in_dt, out_dt):
         t = torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1).copy()).pin_memory()
         return t
 
-    cases = [("dot", (1000, 256), (256, 384)), ("matmul", (5, 136, 128), (5, 128, 72)), ("matmul", (3, 200, 64), (64, 40))]
+    # the fourth and fifth cases have a rhs of 8 MiB or more: it travels in column panels, with
+    # a narrower last panel and a short last row block; in the fifth the lhs is a batch of three
+    k_big = 4096 // np.dtype(O.NP_STORAGE[in_dt]).itemsize
+    cases = [("dot", (1000, 256), (256, 384)), ("matmul", (5, 136, 128), (5, 128, 72)), ("matmul", (3, 200, 64), (64, 40)),
+             ("dot", (700, k_big), (k_big, 2432)), ("matmul", (3, 200, k_big), (k_big, 2048))]
     for kind, ls, rs in cases:
         a, b = storage(ls), storage(rs)
         la, lb = Layout.from_shape(ls), Layout.from_shape(rs)
