@@ -237,7 +237,7 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   if (want_tc) {
     const char* why = "";
     const int r = pb.in_dtype == HODU_DTYPE_F32 ? launch_gemm_f32(pb, st, stream, &why)
-                                                : launch_gemm_tc(pb, st, stream, &why);
+                                                : launch_gemm_tc_splitk(pb, st, stream, &why);
     if (r == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
     if (r < 0) return r;
     // A layout TMA cannot take: with enough work to pay for it, copy the operand(s) first.

@@ -95,6 +95,7 @@ struct Problem {
   const void* bias = nullptr;
   int64_t bias_offset = 0, bias_stride = 1;
   uint32_t bias_flags = 0;
+  bool no_scratch = false;    // the caller forbids stream-ordered scratch (hodu_b200_dot_f32_static)
   bool f32_presplit = false;  // f32 operands already in the three-segment TF32 split form (gemm_f32.cu)
 };
 
@@ -103,6 +104,9 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream);
 // tcgen05 kernel. Returns 1 if the layout cannot be described to TMA (nothing
 // launched, `why` says which rule failed), 0 when launched, <0 on error.
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// The same, with K cut into slices that run as one batched launch plus a reduction when the
+// output alone cannot occupy the GPU (splitk.cu); otherwise exactly launch_gemm_tc.
+int launch_gemm_tc_splitk(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
 // Layout front door (relayout.cu): copies the operands TMA cannot describe into scratch as
 // K-contiguous matrices, then runs the tensor-core kernel.  1 = nothing to fix / not applicable.
 bool tc_operand_describable(const Problem& pb, const Operand& op, bool is_lhs, int esize);

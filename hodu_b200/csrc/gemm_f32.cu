@@ -171,7 +171,7 @@ int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t strea
   q.a = a.out; q.a.ptr = da;
   q.b = b.out; q.b.ptr = db;
   q.f32_presplit = true;
-  return launch_gemm_tc(q, st, stream, why);
+  return launch_gemm_tc_splitk(q, st, stream, why);
 }
 
 // Allocates the scratch on `stream` (stream-ordered pool), runs the split product, frees it.
@@ -244,6 +244,7 @@ extern "C" int hodu_b200_dot_f32_static(int device, void* stream, const void* lh
     return fail(HODU_B200_ERR_INVALID_INPUT, "device %d out of range 0..%d", device, kMaxDevices - 1);
   pb.in_dtype = HODU_DTYPE_F32; pb.out_dtype = HODU_DTYPE_F32;
   pb.a.ptr = lhs; pb.b.ptr = rhs; pb.out = out;
+  pb.no_scratch = true;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   DeviceGuard guard(device);
   if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);

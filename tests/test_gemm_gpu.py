@@ -7,7 +7,8 @@ import numpy as np
 import pytest
 
 from gpu_util import check_close, gpu_matmul
-from hodu_b200 import CudaKernelError, Layout, _lib
+from hodu_b200 import CudaKernelError, DType, Layout, _lib
+from hodu_b200 import kernels as K
 from hodu_b200.op_metadatas import dot_metadata, matmul_metadata
 from oracle import oracle as O
 from test_oracle import KNOWN
@@ -291,3 +292,37 @@ def test_saturation_of_e4m3_output():
         got, _ = gpu_matmul(a, b, md, O.F8E4M3, O.F8E4M3, is_dot=True, path=path)
         g = got.reshape(128, 128)
         assert np.all(g[:, :64] == 0x7E) and np.all(g[:, 64:] == 0xFE)
+
+
+# ---------------------------------------------------------------- split over K for small outputs
+SPLITK = [
+    # M, K, N, in dtype, out dtype, lhs K-contiguous?, rhs N-contiguous?, launches expected
+    (256, 8192, 256, O.BF16, O.BF16, True, True, 2),
+    (256, 8192, 256, O.BF16, O.F32, False, False, 2),     # transposed views of both operands
+    (128, 4096, 192, O.F16, O.F16, True, False, 2),
+    (128, 16384, 64, O.F8E4M3, O.BF16, True, True, 2),
+    (512, 1024, 768, O.F32, O.F32, True, True, 4),         # config 1: two operand splits, product, reduction
+    (256, 8192, 250, O.BF16, O.BF16, True, False, 1),      # N not a multiple of 4: runs whole
+]
+
+
+@pytest.mark.parametrize("case", SPLITK, ids=[f"{c[0]}x{c[1]}x{c[2]}-{DType(c[3])}-{DType(c[4])}-{int(c[5])}{int(c[6])}" for c in SPLITK])
+def test_small_outputs_with_long_k_are_split_over_k(case):
+    m, k, n, in_dt, out_dt, a_kmajor, b_nmajor, launches = case
+    rng = np.random.default_rng(m + k + n)
+    scale = 8.0 if in_dt == O.F8E4M3 else 1.0
+    a = O.narrow((rng.standard_normal((m, k)) * scale).astype(np.float32), in_dt).reshape(m, k)
+    b = O.narrow((rng.standard_normal((k, n)) * scale).astype(np.float32), in_dt).reshape(k, n)
+    la = Layout.from_shape((m, k)) if a_kmajor else Layout.from_shape((k, m)).transpose(0, 1)
+    lb = Layout.from_shape((k, n)) if b_nmajor else Layout.from_shape((n, k)).transpose(0, 1)
+    a_store = a if a_kmajor else np.ascontiguousarray(a.T)
+    b_store = b if b_nmajor else np.ascontiguousarray(b.T)
+    md = dot_metadata(la, lb)
+    scales = (1 / 16, 1 / 4) if in_dt == O.F8E4M3 else (1.0, 1.0)
+    before = K.launch_count()
+    got, taken = gpu_matmul(a_store, b_store, md, in_dt, out_dt, scales=scales, is_dot=True)
+    assert K.launch_count() - before == launches
+    assert taken == K._lib.PATH_TENSOR
+    want = O.matmul(a_store, b_store, md, in_dt, out_dt, scales[0] * scales[1], is_dot=True)
+    tol = {O.F32: 1e-4, O.BF16: 1e-2, O.F16: 1e-2}[out_dt] if in_dt != O.F8E4M3 else 6e-2
+    check_close(got, want, out_dt, tol)

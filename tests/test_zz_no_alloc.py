@@ -54,7 +54,9 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
             K.force_path(prev)
         assert K.last_status(0) == 0
         g, w = got[: m * n].cpu().numpy(), want.cpu().numpy()
-        assert O.rel_err(g, w) <= 1e-6                                        # same kernels, same order of sums
+        # same kernels; the allocating entry point may add the three product terms as separate
+        # K slices (it has scratch for the partial sums), so only the order of the sums differs
+        assert O.rel_err(g, w) <= 2e-5
         assert O.rel_err(g, O.matmul(a, b, md, O.F32, is_dot=True)) <= 1e-4  # and the f32 bar against the oracle
 
 
