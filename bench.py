@@ -47,7 +47,7 @@ CAST_WORKLOADS = {"cast_bf16": ("bf16", 2), "cast_e4m3": ("f8e4m3", 1)}  # desti
 CAST_ELEMS = 67_108_864
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"c2": 402.4e6, "c3": 541.3e6, "c4": 666.0e6, "c5": None, "c1": None,  # profiles/gemm_tc_pair512_configs2_3_4.md
+NCU_TRAFFIC_BYTES = {"c2": 402.4e6, "c3": 483.3e6, "c4": 626.0e6, "c5": 2634.0e6, "c1": None,  # profiles/gemm_tc_pair512_configs2_3_4.md
                      "cast_bf16": 365.0e6, "cast_e4m3": 312.0e6}  # profiles/cast_contig_f32_to_bf16_e4m3_67M_elements.md
 NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0}
 

@@ -270,6 +270,26 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* dst, const uint32_t (&v
 template <int OUT> struct ChunkWords {  // 32-bit words one lane holds for a 32-column chunk
   static constexpr int value = OutBytes<OUT>::value == 4 ? 32 : 16;
 };
+// Two values of a 16-bit output dtype in one word, and back (exact).
+template <int OUT> __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
+  if constexpr (OUT == OUT_BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+template <int OUT> __device__ __forceinline__ void unpack_pair(uint32_t w, float& a, float& b) {
+  if constexpr (OUT == OUT_BF16) {
+    a = __uint_as_float(w << 16);
+    b = __uint_as_float(w & 0xFFFF0000u);
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    a = __low2float(h);
+    b = __high2float(h);
+  }
+}
 template <int OUT>
 __device__ __forceinline__ void pack_chunk(const uint32_t (&v)[32], uint32_t (&pk)[ChunkWords<OUT>::value]) {
   if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
@@ -652,21 +672,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // the accumulator back to the MMA issuer, and only then does the global stores.
       constexpr bool kEarlyRelease = MH == 2 && (OUT == OUT_BF16 || OUT == OUT_F16);
       bool released = false;
-      if (kEarlyRelease && staged) {
+      // SwiGLU in the op-by-op rounding form first rounds gate and up to the storage dtype, so
+      // the two can leave TMEM as packed 16-bit pairs and silu / product run after the release.
+      const bool swiglu_split = SWIGLU && p.swiglu_flags == HODU_B200_SWIGLU_ROUND_EACH_OP;
+      if (kEarlyRelease && staged && (!SWIGLU || swiglu_split)) {
         uint32_t pk[kChunks][16];
+        [[maybe_unused]] uint32_t pu[SWIGLU ? kChunks : 1][16];
 #pragma unroll
         for (uint32_t i = 0; i < kChunks; ++i) {
           const uint32_t c = col_group * kChunks + i;
           if (n0 + c * 32u < p.N) {
             uint32_t v[32];
-            load_chunk(c, v);
-            pack_chunk<OUT>(v, *reinterpret_cast<uint32_t(*)[ChunkWords<OUT>::value]>(&pk[i]));
+            if constexpr (SWIGLU) {
+              tmem_ld_32x32(t_row + c * 32u, v);
+              tmem_wait_ld();
+              pack_chunk<OUT>(v, *reinterpret_cast<uint32_t(*)[ChunkWords<OUT>::value]>(&pk[i]));
+              tmem_ld_32x32(t_row + kOutCols + c * 32u, v);
+              tmem_wait_ld();
+              pack_chunk<OUT>(v, *reinterpret_cast<uint32_t(*)[ChunkWords<OUT>::value]>(&pu[i]));
+            } else {
+              load_chunk(c, v);
+              pack_chunk<OUT>(v, *reinterpret_cast<uint32_t(*)[ChunkWords<OUT>::value]>(&pk[i]));
+            }
           }
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_addr(tmem_empty0 + acc * 8u);
         released = true;
+        if constexpr (SWIGLU) {
+#pragma unroll
+          for (uint32_t i = 0; i < kChunks; ++i) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float g0, g1, u0, u1;
+              unpack_pair<OUT>(pk[i][j], g0, g1);
+              unpack_pair<OUT>(pu[i][j], u0, u1);
+              const float r0 = round_to_storage<OUT>(silu_f32(g0)) * u0;
+              const float r1 = round_to_storage<OUT>(silu_f32(g1)) * u1;
+              pk[i][j] = pack_pair<OUT>(r0, r1);
+            }
+          }
+        }
 #ifdef HODU_TC_PROFILE
         if (!(p.out_vec_ok & 8u))
 #endif
