@@ -37,6 +37,8 @@ template <> struct Conv<float, double> { static __device__ double f(float x) { r
 template <> struct Conv<double, float> { static __device__ float f(double x) { return static_cast<float>(x); } };
 template <> struct Conv<float, int32_t> { static __device__ int32_t f(float x) { return static_cast<int32_t>(x); } };
 template <> struct Conv<int32_t, float> { static __device__ float f(int32_t x) { return static_cast<float>(x); } };
+template <> struct Conv<float, uint32_t> { static __device__ uint32_t f(float x) { return static_cast<uint32_t>(x); } };
+template <> struct Conv<uint32_t, float> { static __device__ float f(uint32_t x) { return static_cast<float>(x); } };
 // Same-type "conversion": the strided -> contiguous copy (`contiguous`), by element width.
 template <> struct Conv<uint8_t, uint8_t> { static __device__ uint8_t f(uint8_t x) { return x; } };
 template <> struct Conv<uint16_t, uint16_t> { static __device__ uint16_t f(uint16_t x) { return x; } };
@@ -166,8 +168,8 @@ int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, s
   const bool known = (src == HODU_DTYPE_F32 && (dst == HODU_DTYPE_BF16 || dst == HODU_DTYPE_F16 || dst == HODU_DTYPE_F8E4M3)) ||
                      (dst == HODU_DTYPE_F32 && (src == HODU_DTYPE_BF16 || src == HODU_DTYPE_F16 || src == HODU_DTYPE_F8E4M3)) ||
                      (src == HODU_DTYPE_I8 && dst == HODU_DTYPE_I32) ||
-                     (src == HODU_DTYPE_F32 && (dst == HODU_DTYPE_F64 || dst == HODU_DTYPE_I32)) ||
-                     (dst == HODU_DTYPE_F32 && (src == HODU_DTYPE_F64 || src == HODU_DTYPE_I32)) ||
+                     (src == HODU_DTYPE_F32 && (dst == HODU_DTYPE_F64 || dst == HODU_DTYPE_I32 || dst == HODU_DTYPE_U32)) ||
+                     (dst == HODU_DTYPE_F32 && (src == HODU_DTYPE_F64 || src == HODU_DTYPE_I32 || src == HODU_DTYPE_U32)) ||
                      (src == dst && dtype_size(src) > 0);
   if (!known) return fail(HODU_B200_ERR_INVALID_KERNEL, "cast: unsupported pair %s -> %s", dtype_name(src), dtype_name(dst));
   // Arguments are valid: only now is the device touched.
@@ -189,6 +191,8 @@ int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, s
   HODU_CAST(HODU_DTYPE_F64, HODU_DTYPE_F32, double, float);
   HODU_CAST(HODU_DTYPE_F32, HODU_DTYPE_I32, float, int32_t);
   HODU_CAST(HODU_DTYPE_I32, HODU_DTYPE_F32, int32_t, float);
+  HODU_CAST(HODU_DTYPE_F32, HODU_DTYPE_U32, float, uint32_t);
+  HODU_CAST(HODU_DTYPE_U32, HODU_DTYPE_F32, uint32_t, float);
 #undef HODU_CAST
   if (src == dst) {
     switch (dtype_size(src)) {

@@ -161,7 +161,8 @@ int hodu_b200_dot_ex(int device, void* stream, uint8_t in_dtype, uint8_t out_dty
  * (crates/hodu_cuda_kernels/src/kernels/ops_cast.rs:27-64) and
  * `hodu_cuda_cast_{src}_to_{dst}` (crates/hodu_cuda_kernels/kernels/ops_cast.cu:7-30)
  * for f32 <-> bf16 | f16 | f8e4m3, i8 -> i32, and the pairs hodu_core wires for CUDA today:
- * f32 <-> f64, f32 <-> i32 (crates/hodu_core/src/be_cuda/storage.rs:652-673).
+ * f32 <-> f64, f32 <-> i32 (crates/hodu_core/src/be_cuda/storage.rs:652-673), plus f32 <-> u32,
+ * the remaining pair of the reference's cast tests (crates/hodu_cuda_kernels/tests/ops_cast.rs:48-89).
  * metadata = [num_els, ndim, shape.., strides.., offset]
  * (crates/hodu_core/src/op_metadatas.rs:1615-1640).
  */

@@ -90,3 +90,31 @@ def test_round_trip_is_idempotent():
         back = run_cast(once, Layout.from_shape(x.shape), dt, O.F32)
         twice = run_cast(back, Layout.from_shape(x.shape), O.F32, dt)
         assert np.array_equal(once, twice)
+
+
+# The reference's six cast known answers (crates/hodu_cuda_kernels/tests/ops_cast.rs:48-89).
+REF_CAST_KNOWN = [
+    ("F32_I32", np.array([1.5, -2.7, 3.2, -4.9], dtype=np.float32), np.array([1, -2, 3, -4], dtype=np.int32)),
+    ("I32_F32", np.array([1, -2, 3, -4], dtype=np.int32), np.array([1.0, -2.0, 3.0, -4.0], dtype=np.float32)),
+    ("F32_U32", np.array([1.5, 2.7, 3.2, 4.9], dtype=np.float32), np.array([1, 2, 3, 4], dtype=np.uint32)),
+    ("U32_F32", np.array([1, 2, 3, 4], dtype=np.uint32), np.array([1.0, 2.0, 3.0, 4.0], dtype=np.float32)),
+    ("F64_F32", np.array([1.5, 2.7, 3.2, 4.9], dtype=np.float64), np.array([1.5, 2.7, 3.2, 4.9], dtype=np.float32)),
+    ("F32_F64", np.array([1.5, 2.7, 3.2, 4.9], dtype=np.float32),
+     np.array([1.5, 2.7, 3.2, 4.9], dtype=np.float32).astype(np.float64)),
+]
+
+
+@pytest.mark.parametrize("case", REF_CAST_KNOWN, ids=[c[0] for c in REF_CAST_KNOWN])
+def test_reference_cast_known_answers(case):
+    import torch
+    name, src, want = case
+    view = {np.dtype(np.uint32): np.int32}
+    s_np = src.view(view.get(src.dtype, src.dtype))
+    d_src = torch.from_numpy(s_np.copy()).to("cuda:0")
+    d_out = torch.zeros(want.size * want.itemsize + 16, dtype=torch.uint8, device="cuda:0")
+    K.call_ops_cast(getattr(K.cast, name), 0, d_src.data_ptr(), d_out.data_ptr(),
+                    cast_metadata(Layout.from_shape(src.shape)), 0)
+    assert K.last_status(0) == 0
+    got = d_out.cpu().numpy()[: want.size * want.itemsize].view(want.dtype)
+    assert np.array_equal(got, want)
+    assert not d_out.cpu().numpy()[want.size * want.itemsize:].any()   # nothing written past the end
