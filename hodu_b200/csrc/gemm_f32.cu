@@ -43,12 +43,12 @@ __device__ __forceinline__ float tf32_round(float x) {
 
 // 32 x 32 tiles, 256 threads (32 x 8).  The source is read along whichever of its two indices
 // is contiguous; the destination is always written along k.
-__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitParams p) {
+__device__ __forceinline__ void split_tf32_body(const SplitParams& p, unsigned block, unsigned blocks) {
   __shared__ float tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const long long per = p.tiles_mn * p.tiles_k;
   const bool k_fast = (p.s_k == 1) || (p.s_mn != 1);
-  for (long long t = blockIdx.x; t < per * p.nb; t += gridDim.x) {
+  for (long long t = block; t < per * p.nb; t += blocks) {
     const long long b = t / per, r = t - b * per;
     const long long mn0 = (r / p.tiles_k) * 32, k0 = (r % p.tiles_k) * 32;
     long long boff = 0, rem = b;
@@ -77,6 +77,13 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitParams p) {
     }
     __syncthreads();
   }
+}
+
+// Both operands of one product in one launch: the first `blocks_a` CTAs split the lhs, the
+// rest the rhs.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitParams pa, const SplitParams pb, unsigned blocks_a) {
+  if (blockIdx.x < blocks_a) split_tf32_body(pa, blockIdx.x, blocks_a);
+  else split_tf32_body(pb, blockIdx.x - blocks_a, gridDim.x - blocks_a);
 }
 
 struct SplitPlan {
@@ -126,16 +133,18 @@ bool plan_split(const Problem& pb, const Operand& op, bool is_lhs, SplitPlan* pl
   return true;
 }
 
-int run_split(const SplitPlan& plan, const void* src, int64_t src_offset, float* dst, DeviceState* st,
-              cudaStream_t stream) {
-  SplitParams sp = plan.sp;
-  sp.src = static_cast<const float*>(src) + src_offset;
-  sp.dst = dst;
-  long long blocks = sp.tiles_mn * sp.tiles_k * sp.nb;
-  const long long cap = static_cast<long long>(st->sm_count) * 32;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) return 0;
-  split_tf32_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sp);
+int run_splits(const SplitPlan& a, const Operand& opa, float* da, const SplitPlan& b, const Operand& opb, float* db,
+               DeviceState* st, cudaStream_t stream) {
+  SplitParams pa = a.sp, pb = b.sp;
+  pa.src = static_cast<const float*>(opa.ptr) + opa.offset; pa.dst = da;
+  pb.src = static_cast<const float*>(opb.ptr) + opb.offset; pb.dst = db;
+  const long long cap = static_cast<long long>(st->sm_count) * 16;
+  auto blocks_of = [&](const SplitParams& p) {
+    long long n = p.tiles_mn * p.tiles_k * p.nb;
+    return n > cap ? cap : (n < 1 ? 1 : n);
+  };
+  const unsigned na = static_cast<unsigned>(blocks_of(pa)), nb = static_cast<unsigned>(blocks_of(pb));
+  split_tf32_kernel<<<na + nb, 256, 0, stream>>>(pa, pb, na);
   HODU_CUDA_TRY(cudaGetLastError(), HODU_B200_ERR_LAUNCH);
   count_launch();
   return 0;
@@ -162,9 +171,7 @@ int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t strea
   if (a_bytes + b.bytes > scratch_bytes) { *why = "scratch too small"; return 1; }
   float* da = static_cast<float*>(scratch);
   float* db = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + a_bytes);
-  int r = run_split(a, pb.a.ptr, pb.a.offset, da, st, stream);
-  if (r) return r;
-  r = run_split(b, pb.b.ptr, pb.b.offset, db, st, stream);
+  const int r = run_splits(a, pb.a, da, b, pb.b, db, st, stream);
   if (r) return r;
   Problem q = pb;
   q.K = 3 * pb.K;

@@ -301,7 +301,7 @@ SPLITK = [
     (256, 8192, 256, O.BF16, O.F32, False, False, 2),     # transposed views of both operands
     (128, 4096, 192, O.F16, O.F16, True, False, 2),
     (128, 16384, 64, O.F8E4M3, O.BF16, True, True, 2),
-    (512, 1024, 768, O.F32, O.F32, True, True, 4),         # config 1: two operand splits, product, reduction
+    (512, 1024, 768, O.F32, O.F32, True, True, 3),         # config 1: operand split, product, reduction
     (256, 8192, 250, O.BF16, O.BF16, True, False, 1),      # N not a multiple of 4: runs whole
 ]
 
