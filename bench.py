@@ -349,6 +349,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU runs the whole configuration; strong: the one configuration is sharded over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--all-gather", action="store_true",
+                    help="N > 1: also time an NCCL all-gather of the outputs (reported separately)")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="after the timed region: per-step best/median and a back-to-back run of this length (0 = skip)")
     args = ap.parse_args()
@@ -413,6 +415,29 @@ def main():
     is_cast = args.workload in CAST_WORKLOADS
     per_unit = 1e9 if is_cast else 1e12   # casts count bytes (GB/s), products count flops (TFLOP/s)
     value = total_flops / (ms_per_step * 1e-3) / per_unit
+
+    # ---- optional: all-gather of the output over NCCL, timed separately (N > 1) -----------------
+    gather = None
+    if world > 1 and args.all_gather and hasattr(wl, "out"):
+        flat = wl.out.reshape(-1)
+        full = torch.empty(flat.numel() * world, dtype=flat.dtype, device=dev)
+        for _ in range(2):
+            dist.all_gather_into_tensor(full, flat)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        g0.record(stream)
+        for _ in range(reps):
+            dist.all_gather_into_tensor(full, flat)
+        g1.record(stream)
+        torch.cuda.synchronize(dev)
+        gt = torch.tensor([g0.elapsed_time(g1) / reps], dtype=torch.float64, device=dev)
+        dist.all_reduce(gt, op=dist.ReduceOp.MAX)
+        g_ms = float(gt.item())
+        nbytes = flat.numel() * flat.element_size()
+        gather = {"ms": g_ms, "bytes_per_rank": int(nbytes),
+                  "bus_gbs": nbytes * (world - 1) / (g_ms * 1e-3) / 1e9,
+                  "note": "ncclAllGather of every rank's output into a full copy on every rank; not part of `value`"}
 
     # ---- spread and a sustained figure (1 GPU only; outside the timed region above) -------------
     detail = None
@@ -508,6 +533,8 @@ def main():
         line["e2e"] = e2e
     if detail is not None:
         line["spread"] = detail
+    if gather is not None:
+        line["all_gather"] = gather
     if world == 1 and not args.no_cpu_baseline:
         v, kind, cores, sample, secs = (cpu_reference_cast_rate if is_cast else cpu_reference_rate)(args.workload, 15.0)
         line["cpu_baseline"] = {"value": v, "unit": "GB/s" if is_cast else "TFLOP/s", "cores": cores, "kind": kind,
