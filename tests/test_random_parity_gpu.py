@@ -178,3 +178,30 @@ def test_random_linear_cases(seed):
     want = O.linear(O.widen(x, dt).reshape(*batch, m, k), O.widen(w, dt).reshape(n, k).T, bias, dt,
                     round_each_op=(flags == _lib.LINEAR_ROUND_EACH_OP))
     assert O.rel_err(O.widen(got, dt), O.widen(want, dt)) <= TOL[dt]
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_random_large_tails_on_the_pair_forms(seed):
+    """Extents of 300..2100 that are multiples of nothing in particular, on the CTA-pair tile
+    forms (256x256 and 512x256) and the automatic choice: M / N / K tails of every size."""
+    rng = np.random.default_rng(5000 + seed)
+    in_dt, out_dt = [(O.BF16, O.BF16), (O.I8, O.I32), (O.F8E4M3, O.BF16), (O.F16, O.F32)][seed % 4]
+    esz = np.dtype(O.NP_STORAGE[in_dt]).itemsize
+    unit = 16 // esz
+    m = int(rng.integers(300, 2100))
+    k = int(rng.integers(300, 2100)) // unit * unit        # pitches TMA can take
+    n = int(rng.integers(300, 2100)) // 8 * 8
+    b_kmajor = bool(rng.integers(0, 2))
+    if esz == 1 and not b_kmajor:
+        n = n // 16 * 16
+    a = values(rng, m * k, in_dt)
+    b = values(rng, k * n, in_dt)
+    la = Layout.from_shape((m, k))
+    lb = Layout.from_shape((n, k)).transpose(0, 1) if b_kmajor else Layout.from_shape((k, n))
+    md = dot_metadata(la, lb)
+    scales = (0.125, 0.25) if in_dt == O.F8E4M3 else (1.0, 1.0)
+    path = [_lib.PATH_AUTO, _lib.PATH_TENSOR_2CTA, _lib.PATH_TENSOR_2CTA_512][seed % 3]
+    got, taken = gpu_matmul(a, b, md, in_dt, out_dt, scales=scales, is_dot=True, path=path)
+    assert taken == _lib.PATH_TENSOR
+    want = O.matmul(a, b, md, in_dt, out_dt, scales[0] * scales[1], is_dot=True)
+    check_close(got, want, out_dt, TOL.get(out_dt, 0))
