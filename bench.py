@@ -43,13 +43,22 @@ WORKLOADS = {
     "cast_bf16": "cast f32 -> bf16 of 67,108,864 contiguous elements (input preparation of one config 2 operand)",
     "cast_e4m3": "cast f32 -> f8e4m3 of 67,108,864 contiguous elements (input preparation of one config 3 operand)",
 }
+# the widened rows (not BASELINE configs): one representative shape each
+WIDENED = {
+    "linear": "Linear with bias, X[8192,4096] . W[4096,4096]^T + b[4096], bf16 (hodu_nn::Linear forward, one launch)",
+    "einsum_qk": "einsum bhqd,bhkd->bhqk, b=4 h=16 q=k=2048 d=128, bf16 (attention scores; 512 MiB written: HBM-bound)",
+    "conv3x3": "conv2d NCHW batch 32, 64->64 channels, 56x56, 3x3, padding 1, bf16 (im2col + one batched product)",
+}
+WORKLOADS.update(WIDENED)
 CAST_WORKLOADS = {"cast_bf16": ("bf16", 2), "cast_e4m3": ("f8e4m3", 1)}  # destination dtype, its size
 CAST_ELEMS = 67_108_864
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
 # profiles/ (None until a capture of that workload exists).
 NCU_TRAFFIC_BYTES = {"c2": 402.4e6, "c3": 483.3e6, "c4": 626.0e6, "c5": 2634.0e6, "c1": None,  # profiles/gemm_tc_pair512_configs2_3_4.md
+                     "linear": None, "einsum_qk": None, "conv3x3": None,
                      "cast_bf16": 365.0e6, "cast_e4m3": 312.0e6}  # profiles/cast_contig_f32_to_bf16_e4m3_67M_elements.md
-NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0}
+NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0,
+                       "linear": 2250.0, "einsum_qk": 2250.0, "conv3x3": 2250.0}
 
 
 def measured_peaks():
@@ -157,7 +166,10 @@ def cpu_reference_rate(workload: str, budget_s: float):
         flops = 2.0 * nb * d ** 3
         sample = f"{nb} of 16 batches of config 2 (operands widened to f32 beforehand, one hodu_cpu_matmul_f32 call)"
     else:
-        shapes = {"c1": (512, 1024, 768), "c3": (8192, 8192, 8192), "c4": (8192, 8192, 8192), "c5": (16384, 4096, 14336)}
+        # the widened rows are timed as the f32 product of their GEMM shape (the reference's CPU
+        # conv2d / einsum kernels are scalar loops; its OpenBLAS build unfolds and calls sgemm too)
+        shapes = {"c1": (512, 1024, 768), "c3": (8192, 8192, 8192), "c4": (8192, 8192, 8192), "c5": (16384, 4096, 14336),
+                  "linear": (8192, 4096, 4096), "einsum_qk": (2048, 128, 2048), "conv3x3": (64, 576, 3136)}
         m, k, n = shapes[workload]
         b = rng.standard_normal((k, n), dtype=np.float32)
         probe_rows = min(m, 512)
@@ -260,6 +272,7 @@ class Workload:
         from hodu_b200.tensor import Tensor
 
         self.name, self.K, self.torch = name, K, torch
+        self.bound, self.alg_bytes = ("hbm" if name in CAST_WORKLOADS else "tensor"), None
         d0 = dev.index or 0
 
         def cast_on_device(x32: np.ndarray, dt):
@@ -314,6 +327,40 @@ class Workload:
             self.flops, self.dtype, self.launches = float(S.FLOPS[5]) * (hi - lo) / 16384.0, "bf16", 2
             self.step = lambda: self.mlp.forward(self.x)
             self.md = None
+        elif name == "linear":
+            g = torch.Generator(device=dev).manual_seed(11)
+            m, k, n = 8192, 4096, 4096
+            x = Tensor.from_torch((torch.randn(m, k, generator=g, device=dev)).bfloat16())
+            w = Tensor.from_torch((torch.randn(n, k, generator=g, device=dev) / 64).bfloat16())
+            bias = Tensor.from_torch(torch.randn(n, generator=g, device=dev).bfloat16())
+            self.layer = Linear(w, bias)
+            self.flops, self.dtype, self.launches = 2.0 * m * n * k, "bf16", 1
+            self.step = lambda: self.layer.forward(x)
+        elif name == "einsum_qk":
+            from hodu_b200.tensor import einsum
+            g = torch.Generator(device=dev).manual_seed(12)
+            b_, h_, q_, d_ = 4, 16, 2048, 128
+            qt = Tensor.from_torch(torch.randn(b_, h_, q_, d_, generator=g, device=dev).bfloat16())
+            kt = Tensor.from_torch(torch.randn(b_, h_, q_, d_, generator=g, device=dev).bfloat16())
+            self.flops, self.dtype, self.launches = 2.0 * b_ * h_ * q_ * q_ * d_, "bf16", 1
+            self.alg_bytes = 2.0 * (2 * b_ * h_ * q_ * d_ + b_ * h_ * q_ * q_)   # Q and K read, scores written
+            self.bound = "hbm"
+            self.step = lambda: einsum("bhqd,bhkd->bhqk", [qt, kt])
+        elif name == "conv3x3":
+            from hodu_b200.op_metadatas import conv2d_metadata
+            g = torch.Generator(device=dev).manual_seed(13)
+            b_, ci, co, hw = 32, 64, 64, 56
+            self.a = torch.randn(b_ * ci * hw * hw, generator=g, device=dev).bfloat16()
+            self.b = (torch.randn(co * ci * 9, generator=g, device=dev) / 24).bfloat16()
+            self.md = conv2d_metadata(b_, ci, co, (hw, hw), (3, 3), (1, 1), (1, 1))
+            self.out = torch.empty(self.md[0], dtype=torch.bfloat16, device=dev)
+            self.flops, self.dtype, self.launches = 2.0 * self.md[0] * ci * 9, "bf16", 2
+            col = b_ * ci * 9 * hw * hw
+            # input read, unfolded copy written then read by the product, weights, output written
+            self.alg_bytes = 2.0 * (b_ * ci * hw * hw + 2 * col + co * ci * 9 + self.md[0])
+            self.bound = "hbm"
+            self.step = lambda: K.call_ops_conv(K.conv2d.BF16, d0, self.a.data_ptr(), self.b.data_ptr(),
+                                                self.out.data_ptr(), self.md, stream_ptr)
         elif name in CAST_WORKLOADS:
             # HBM-bound leg: algorithmic bytes per element = 4 (f32 read) + size of the destination.
             dst_name, dst_size = CAST_WORKLOADS[name]
@@ -497,10 +544,11 @@ def main():
 
     peaks = measured_peaks()
     timed_s = ms_total * 1e-3
-    if is_cast:
+    hbm_bound = wl.bound == "hbm"
+    if hbm_bound:
         peak, peak_src = peaks["hbm_gbs"], (f"{peaks['source']} copy bandwidth (MEASURED_PEAKS.json)"
                                             if peaks["source"] == "measured" else "fallback 6650 GB/s")
-    elif args.workload in ("c2", "c5"):
+    elif args.workload in ("c2", "c5", "linear"):
         # cuBLAS burst for a short region at full clocks; its sustained figure once the region is
         # long or the power cap was seen active while it ran
         clk = clocks.summary()
@@ -509,6 +557,8 @@ def main():
     else:
         peak, peak_src = NOMINAL_PEAK_TFLOPS[args.workload], "nominal dense peak for this dtype (no measured figure for it)"
     achieved = wl.flops / (ms_total / args.steps * 1e-3) / per_unit  # this rank, per launch group
+    if hbm_bound and not is_cast:   # a product whose algorithmic bytes, not flops, bound it
+        achieved = wl.alg_bytes / (ms_total / args.steps * 1e-3) / 1e9
     unit = "GB/s" if is_cast else ("TFLOP/s" if args.workload != "c4" else "TOP/s")
     line = {
         "metric": "cast throughput" if is_cast else "matmul throughput", "value": value, "unit": unit,
@@ -517,16 +567,18 @@ def main():
         "config": {"workload": WORKLOADS[args.workload],
                    "per_gpu": ("1/N of the configuration: whole batches (c2) or rows of A / tokens, B and weights replicated, no collective"
                                if strong else "the whole configuration on every GPU (independent batches / rows, no collective)"),
-                   "l2": "operands + output exceed the 126 MB L2 (no flush needed)" if args.workload != "c1" else "fits in L2 (latency-bound case)",
+                   "l2": ("operands + output exceed the 126 MB L2 (no flush needed)" if args.workload not in ("c1", "conv3x3")
+                          else "fits in L2 (latency-bound case)" if args.workload == "c1"
+                          else "input 12.8 MB fits in L2; the 115.6 MB unfolded copy written and read every step does not"),
                    "timing": "CUDA events on the launching stream around all timed steps, max over ranks"},
         "clocks": clocks.summary(),
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm" if is_cast else "tensor", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s" if is_cast else "TFLOP/s", "frac": achieved / peak,
+        "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak,
+                     "unit": "GB/s" if hbm_bound else "TFLOP/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES[args.workload], "peak_source": peak_src},
     }
-    if is_cast:
-        line["roofline"]["algorithmic_bytes_per_launch"] = wl.flops
+    if hbm_bound:
+        line["roofline"]["algorithmic_bytes_per_step"] = wl.flops if is_cast else wl.alg_bytes
     else:
         line["roofline"]["frac_of_nominal"] = achieved / NOMINAL_PEAK_TFLOPS[args.workload]
     if e2e is not None:

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libhodu_b200.so")
+# HODU_B200_LIB points the binding at another build of the same library (A/B comparisons).
+LIB_PATH = os.environ.get("HODU_B200_LIB") or os.path.join(_HERE, "lib", "libhodu_b200.so")
 
 # Every symbol include/hodu_b200.h declares: name -> (restype, argtypes)
 _vp, _sz, _u8, _u32, _i, _f = C.c_void_p, C.c_size_t, C.c_uint8, C.c_uint32, C.c_int, C.c_float

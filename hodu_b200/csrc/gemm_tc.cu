@@ -1096,7 +1096,13 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
       const double mma_clk = (c == 256 ? 128.0 : (c == 128 ? 64.0 : 50.0)) * 4.0 * (f == 2 ? 2.0 : 1.0);
       const double bytes = (f == 2 ? 32768.0 : 16384.0) + (f ? 128.0 : c) * 128.0;
       const double kblock = 1.08 * (mma_clk > bytes / 50.0 ? mma_clk : bytes / 50.0);
-      const double tile_clk = k_blocks_d * kblock + (f == 2 ? 8000.0 : 0.0) + 1500.0;
+      // Short-K tiles are bound by draining and storing the output instead: measured on
+      // 128-deep bf16 products, cycles per 64 KB of output one CTA stores: 4400 (one CTA per
+      // tile), 5500 (CTA pairs, whose per-tile handshakes cross the cluster).
+      const double out_bytes_cta = 128.0 * (f == 2 ? 2.0 : 1.0) * static_cast<double>(oc) * dtype_size(pb.out_dtype);
+      const double drain_clk = (f ? 5500.0 : 4400.0) * out_bytes_cta / 65536.0;
+      const double main_clk = k_blocks_d * kblock + (f == 2 ? 8000.0 : 0.0) + 1500.0;
+      const double tile_clk = main_clk > drain_clk ? main_clk : drain_clk;
       const double t = static_cast<double>((tiles + units - 1) / units) * tile_clk;
       if (t < best) { best = t; form = f; bn = c; }
     };
