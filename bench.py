@@ -272,7 +272,7 @@ class Workload:
         from hodu_b200.tensor import Tensor
 
         self.name, self.K, self.torch = name, K, torch
-        self.bound, self.alg_bytes = ("hbm" if name in CAST_WORKLOADS else "tensor"), None
+        self.bound, self.alg_bytes, self.write_bytes = ("hbm" if name in CAST_WORKLOADS else "tensor"), None, None
         d0 = dev.index or 0
 
         def cast_on_device(x32: np.ndarray, dt):
@@ -344,6 +344,7 @@ class Workload:
             kt = Tensor.from_torch(torch.randn(b_, h_, q_, d_, generator=g, device=dev).bfloat16())
             self.flops, self.dtype, self.launches = 2.0 * b_ * h_ * q_ * q_ * d_, "bf16", 1
             self.alg_bytes = 2.0 * (2 * b_ * h_ * q_ * d_ + b_ * h_ * q_ * q_)   # Q and K read, scores written
+            self.write_bytes = 2.0 * b_ * h_ * q_ * q_
             self.bound = "hbm"
             self.step = lambda: einsum("bhqd,bhkd->bhqk", [qt, kt])
         elif name == "conv3x3":
@@ -358,6 +359,7 @@ class Workload:
             col = b_ * ci * 9 * hw * hw
             # input read, unfolded copy written then read by the product, weights, output written
             self.alg_bytes = 2.0 * (b_ * ci * hw * hw + 2 * col + co * ci * 9 + self.md[0])
+            self.write_bytes = 2.0 * (col + self.md[0])
             self.bound = "hbm"
             self.step = lambda: K.call_ops_conv(K.conv2d.BF16, d0, self.a.data_ptr(), self.b.data_ptr(),
                                                 self.out.data_ptr(), self.md, stream_ptr)
@@ -372,6 +374,7 @@ class Workload:
             self.md = cast_metadata(Layout.from_shape((CAST_ELEMS,)))
             kern = getattr(K.cast, f"F32_{dst_name.upper()}")
             self.flops, self.dtype, self.launches = float(CAST_ELEMS) * (4 + dst_size), f"f32->{dst_name}", 1
+            self.write_bytes = float(CAST_ELEMS) * dst_size
             self.step = lambda: K.call_ops_cast(kern, d0, self.a.data_ptr(), self.out.data_ptr(), self.md, stream_ptr)
         else:
             raise SystemExit(f"unknown workload {name}")
@@ -579,6 +582,22 @@ def main():
     }
     if hbm_bound:
         line["roofline"]["algorithmic_bytes_per_step"] = wl.flops if is_cast else wl.alg_bytes
+        # HBM takes pure writes more slowly than a copy's mix of reads and writes: time a plain fill of
+        # 512 MiB here and now, and say how the bytes this workload WRITES compare with that rate
+        buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            buf.fill_(1)
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record(stream)
+        for _ in range(10):
+            buf.fill_(1)
+        w1.record(stream)
+        torch.cuda.synchronize(dev)
+        write_peak = 10 * buf.numel() / (w0.elapsed_time(w1) * 1e-3) / 1e9
+        written = wl.write_bytes / (ms_total / args.steps * 1e-3) / 1e9
+        line["roofline"].update({"write_peak_gbs": write_peak, "written_gbs": written,
+                                 "written_frac_of_write_peak": written / write_peak,
+                                 "write_peak_source": "torch fill_ of 512 MiB timed in this run"})
     else:
         line["roofline"]["frac_of_nominal"] = achieved / NOMINAL_PEAK_TFLOPS[args.workload]
     if e2e is not None:

@@ -80,53 +80,55 @@ __global__ void __launch_bounds__(256) im2col_kernel(const Im2colParams p) {
 
 // Unit stride and dilation along the width: the KW col rows of one (ic, kh) read overlapping
 // windows of the same input row, so one thread loads VEC + KW - 1 neighbours once and writes KW
-// vectors from them.  Same grid shape as above with (ic, kh) pairs in place of col rows.
+// vectors from them.  The 256 threads of a CTA are blockDim.x along the columns times blockDim.y
+// (ic, kh) pairs: as many threads along a row as it has vectors (up to all 256), so that long
+// rows are written in long contiguous runs (4 KB per pass) and short rows still fill the CTA.
 template <typename T, int VEC, int KW>
 __global__ void __launch_bounds__(256) im2col_unit_kernel(const Im2colParams p) {
-  const int n0 = (blockIdx.x * 32 + threadIdx.x) * VEC;
-  if (n0 >= p.npitch) return;
-  const int oh0 = n0 / p.ow, ow0 = n0 - oh0 * p.ow;
-  const bool one_row = ow0 + VEC <= p.ow && n0 + VEC <= p.N;
   const int pairs = p.cin * p.kh;
-  for (int img = blockIdx.z; img < p.images; img += gridDim.z) {
-    for (int r = blockIdx.y * 8 + threadIdx.y; r < pairs; r += gridDim.y * 8) {
+  for (int img = blockIdx.y; img < p.images; img += gridDim.y) {
+    for (int r = blockIdx.x * blockDim.y + threadIdx.y; r < pairs; r += gridDim.x * blockDim.y) {
       const int kh = r % p.kh, ic = r / p.kh;
       const T* src = static_cast<const T*>(p.in) + (static_cast<size_t>(img) * p.cin + ic) * p.h * p.w;
       const int ih_off = kh * p.dh - p.ph;
-      T* dst = static_cast<T*>(p.col) + (static_cast<size_t>(img) * p.K + static_cast<size_t>(r) * KW) * p.npitch + n0;
-      if (one_row) {
-        const int ih = oh0 * p.sh + ih_off, iw_base = ow0 - p.pw;
-        const bool row_ok = static_cast<unsigned>(ih) < static_cast<unsigned>(p.h);
-        const T* row = src + (row_ok ? ih : 0) * p.w;
-        T win[VEC + KW - 1];
+      T* dst_row = static_cast<T*>(p.col) + (static_cast<size_t>(img) * p.K + static_cast<size_t>(r) * KW) * p.npitch;
+      for (int n0 = threadIdx.x * VEC; n0 < p.npitch; n0 += blockDim.x * VEC) {
+        const int oh0 = n0 / p.ow, ow0 = n0 - oh0 * p.ow;
+        T* dst = dst_row + n0;
+        if (ow0 + VEC <= p.ow && n0 + VEC <= p.N) {   // VEC neighbours in one input row
+          const int ih = oh0 * p.sh + ih_off, iw_base = ow0 - p.pw;
+          const bool row_ok = static_cast<unsigned>(ih) < static_cast<unsigned>(p.h);
+          const T* row = src + (row_ok ? ih : 0) * p.w;
+          T win[VEC + KW - 1];
 #pragma unroll
-        for (int i = 0; i < VEC + KW - 1; ++i) {
-          const int iw = iw_base + i;
-          win[i] = (row_ok && static_cast<unsigned>(iw) < static_cast<unsigned>(p.w)) ? row[iw] : T(0.0f);
-        }
-#pragma unroll
-        for (int kw = 0; kw < KW; ++kw) {
-          alignas(16) T v[VEC];
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) v[j] = win[kw + j];
-          *reinterpret_cast<uint4*>(dst + static_cast<size_t>(kw) * p.npitch) = *reinterpret_cast<const uint4*>(v);
-        }
-      } else {
-#pragma unroll
-        for (int kw = 0; kw < KW; ++kw) {
-          int oh = oh0, ow = ow0;
-          alignas(16) T v[VEC];
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) {
-            T x = T(0.0f);
-            const int ih = oh * p.sh + ih_off, iw = ow + kw - p.pw;
-            if (n0 + j < p.N && static_cast<unsigned>(ih) < static_cast<unsigned>(p.h) &&
-                static_cast<unsigned>(iw) < static_cast<unsigned>(p.w))
-              x = src[ih * p.w + iw];
-            v[j] = x;
-            if (++ow == p.ow) { ow = 0; ++oh; }
+          for (int i = 0; i < VEC + KW - 1; ++i) {
+            const int iw = iw_base + i;
+            win[i] = (row_ok && static_cast<unsigned>(iw) < static_cast<unsigned>(p.w)) ? row[iw] : T(0.0f);
           }
-          *reinterpret_cast<uint4*>(dst + static_cast<size_t>(kw) * p.npitch) = *reinterpret_cast<const uint4*>(v);
+#pragma unroll
+          for (int kw = 0; kw < KW; ++kw) {
+            alignas(16) T v[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[j] = win[kw + j];
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(kw) * p.npitch) = *reinterpret_cast<const uint4*>(v);
+          }
+        } else {
+#pragma unroll
+          for (int kw = 0; kw < KW; ++kw) {
+            int oh = oh0, ow = ow0;
+            alignas(16) T v[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+              T x = T(0.0f);
+              const int ih = oh * p.sh + ih_off, iw = ow + kw - p.pw;
+              if (n0 + j < p.N && static_cast<unsigned>(ih) < static_cast<unsigned>(p.h) &&
+                  static_cast<unsigned>(iw) < static_cast<unsigned>(p.w))
+                x = src[ih * p.w + iw];
+              v[j] = x;
+              if (++ow == p.ow) { ow = 0; ++oh; }
+            }
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(kw) * p.npitch) = *reinterpret_cast<const uint4*>(v);
+          }
         }
       }
     }
@@ -137,16 +139,23 @@ template <typename T, int VEC>
 int launch_im2col(const Im2colParams& p, cudaStream_t stream) {
   if (p.images <= 0 || p.K <= 0 || p.npitch <= 0) return 0;
   const bool unit = p.sw == 1 && p.dw == 1 && (p.kw == 3 || p.kw == 5 || p.kw == 7);
-  const int rows = unit ? p.cin * p.kh : p.K;
-  const int row_groups = (rows + 7) / 8;
-  dim3 grid(static_cast<unsigned>((p.npitch + VEC * 32 - 1) / (VEC * 32)),
-            static_cast<unsigned>(row_groups < 65535 ? row_groups : 65535),
-            static_cast<unsigned>(p.images < 65535 ? p.images : 65535));
-  const dim3 block(32, 8, 1);
-  if (unit && p.kw == 3) im2col_unit_kernel<T, VEC, 3><<<grid, block, 0, stream>>>(p);
-  else if (unit && p.kw == 5) im2col_unit_kernel<T, VEC, 5><<<grid, block, 0, stream>>>(p);
-  else if (unit) im2col_unit_kernel<T, VEC, 7><<<grid, block, 0, stream>>>(p);
-  else im2col_kernel<T, VEC><<<grid, block, 0, stream>>>(p);
+  if (unit) {
+    const int pairs = p.cin * p.kh, vectors = (p.npitch + VEC - 1) / VEC;
+    int tx = 32;
+    while (tx < 256 && tx < vectors) tx *= 2;
+    const dim3 block(tx, 256 / tx, 1);
+    const int groups = (pairs + static_cast<int>(block.y) - 1) / static_cast<int>(block.y);
+    dim3 grid(static_cast<unsigned>(groups < 65535 ? groups : 65535), static_cast<unsigned>(p.images < 65535 ? p.images : 65535), 1);
+    if (p.kw == 3) im2col_unit_kernel<T, VEC, 3><<<grid, block, 0, stream>>>(p);
+    else if (p.kw == 5) im2col_unit_kernel<T, VEC, 5><<<grid, block, 0, stream>>>(p);
+    else im2col_unit_kernel<T, VEC, 7><<<grid, block, 0, stream>>>(p);
+  } else {
+    const int row_groups = (p.K + 7) / 8;
+    dim3 grid(static_cast<unsigned>((p.npitch + VEC * 32 - 1) / (VEC * 32)),
+              static_cast<unsigned>(row_groups < 65535 ? row_groups : 65535),
+              static_cast<unsigned>(p.images < 65535 ? p.images : 65535));
+    im2col_kernel<T, VEC><<<grid, dim3(32, 8, 1), 0, stream>>>(p);
+  }
   HODU_CUDA_TRY(cudaGetLastError(), HODU_B200_ERR_LAUNCH);
   count_launch();
   return 0;
