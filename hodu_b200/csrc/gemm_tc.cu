@@ -1103,7 +1103,9 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
       const double drain_clk = (f ? 5500.0 : 4400.0) * out_bytes_cta / 65536.0;
       const double main_clk = k_blocks_d * kblock + (f == 2 ? 8000.0 : 0.0) + 1500.0;
       const double tile_clk = main_clk > drain_clk ? main_clk : drain_clk;
-      const double t = static_cast<double>((tiles + units - 1) / units) * tile_clk;
+      // CTA pairs pay a fixed price per launch (cluster launch, cross-CTA set-up and teardown):
+      // measured on 1536^3 .. 3072 x 768 x 3072 products, where one CTA per tile wins by 5-15 %.
+      const double t = static_cast<double>((tiles + units - 1) / units) * tile_clk + (f ? 12000.0 : 0.0);
       if (t < best) { best = t; form = f; bn = c; }
     };
     const bool allow_pair = forced != HODU_B200_PATH_TENSOR_1CTA && st->sm_count >= 2;

@@ -11,6 +11,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace hodu_b200 {
@@ -77,13 +79,21 @@ int pick_splits(const Problem& pb, const DeviceState* st) {
   }
   if (pb.out_dtype != HODU_DTYPE_F32 && pb.out_dtype != HODU_DTYPE_BF16 && pb.out_dtype != HODU_DTYPE_F16) return 1;
   if (pb.N % 4 != 0) return 1;
-  const long long tiles = ((pb.M + 127) / 128) * ((pb.N + 63) / 64);
+  // Worth it when even 128 x 256 tiles would leave half of the SMs idle; as many slices as bring
+  // the count of such tiles up to the SM count (at most 8, at least eight k-blocks each).
+  const long long tiles = ((pb.M + 127) / 128) * ((pb.N + 255) / 256);
   if (tiles * 2 > st->sm_count) return 1;
   const long long k_blocks = pb.K * esize / 128;
   long long s = st->sm_count / tiles;
   if (s > 8) s = 8;
   if (s > k_blocks / 8) s = k_blocks / 8;       // at least eight k-blocks per slice
-  for (; s >= 2; --s)
+  if (const char* e = getenv("HODU_B200_SPLITK")) {   // tuning aid: upper bound on the slices
+    const long long cap = atoi(e);
+    if (cap >= 1 && s > cap) s = cap;
+  }
+  // Two slices do not pay for the partial sums and the second launch (measured on 1024^3 and
+  // 1536^3: 30 % and 20 % slower than the whole product); three or more do.
+  for (; s >= 3; --s)
     if (pb.K % s == 0 && (pb.K / s * esize) % 128 == 0) return static_cast<int>(s);
   return 1;
 }
