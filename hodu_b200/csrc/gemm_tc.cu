@@ -89,6 +89,7 @@ struct OperandLoad {
 struct TcParams {
   uint32_t M, N, K;
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks, group_m;
+  uint32_t k_gen;         // k-blocks per accumulator generation (== k_blocks: one generation per tile)
   uint32_t bdim1, bdim2;  // batch = (b0 * bdim1 + b1) * bdim2 + b2
   uint32_t bk;            // K elements per stage (128 bytes worth)
   OperandLoad a, b;
@@ -313,7 +314,7 @@ template <int KWORDS>
 __device__ __forceinline__ void store_packed_staged(uint8_t* out_tile, unsigned long long pitch_bytes,
                                                     uint32_t row0, uint32_t rows_total, uint32_t col_byte0,
                                                     uint32_t row_bytes_total, const uint32_t (&pk)[KWORDS],
-                                                    uint32_t stage, uint32_t lane) {
+                                                    uint32_t stage, uint32_t lane, bool add_f32 = false) {
   const uint32_t wsw = (lane >> 1) & 3u;  // swizzle of the row this lane writes
 #pragma unroll
   for (int g = 0; g < KWORDS / 16; ++g) {  // groups of 64 bytes per row
@@ -332,9 +333,17 @@ __device__ __forceinline__ void store_packed_staged(uint8_t* out_tile, unsigned 
       const uint32_t addr = stage + r * 64u + ((seg ^ ((r >> 1) & 3u)) << 4);
       asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
       const uint32_t cb = col_byte0 + static_cast<uint32_t>(g) * 64u + seg * 16u;
-      if (row0 + r < rows_total && cb < row_bytes_total)
-        *reinterpret_cast<uint4*>(out_tile + static_cast<unsigned long long>(row0 + r) * pitch_bytes + cb) =
-            make_uint4(x0, x1, x2, x3);
+      if (row0 + r < rows_total && cb < row_bytes_total) {
+        uint4* dst = reinterpret_cast<uint4*>(out_tile + static_cast<unsigned long long>(row0 + r) * pitch_bytes + cb);
+        if (add_f32) {  // a later generation of an f32 tile: add to what the earlier ones stored
+          const uint4 old = *dst;
+          x0 = __float_as_uint(__uint_as_float(old.x) + __uint_as_float(x0));
+          x1 = __float_as_uint(__uint_as_float(old.y) + __uint_as_float(x1));
+          x2 = __float_as_uint(__uint_as_float(old.z) + __uint_as_float(x2));
+          x3 = __float_as_uint(__uint_as_float(old.w) + __uint_as_float(x3));
+        }
+        *dst = make_uint4(x0, x1, x2, x3);
+      }
     }
     __syncwarp();
   }
@@ -437,6 +446,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int kStageB = Cfg::kStageB;
   constexpr int CG = PAIR ? 2 : 1;
   constexpr bool kIntAcc = (KIND == KIND_I8);
+  // Only the f32 path (split TF32 operands) cuts a tile's K into accumulator generations; for
+  // every other kind the generation loops below run once and fold away at compile time.
+  constexpr bool kGenerations = (KIND == KIND_TF32);
   constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
   constexpr uint32_t kTileM = PAIR ? 256u * MH : 128u;
 
@@ -516,13 +528,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t idesc = p.idesc, k_blocks = p.k_blocks;
       uint32_t a_lo = a_lo0, b_lo = b_lo0;  // descriptor low words of the current stage
       uint32_t full_bar = smem_u32(&tail->full[0]), empty_bar = smem_u32(&tail->empty[0]);
-      for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step, ++lt) {
-        // MH == 1: the two accumulators alternate between tiles (double buffer).
-        // MH == 2: one tile fills both, accumulator h holding M-half h.
+      for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step) {
+      uint32_t kb0 = 0;
+      do {
+        // One accumulator generation: the whole tile, or (long f32 products) a run of k_gen
+        // k-blocks whose sum the epilogue adds to the output before the next run starts afresh.
+        // MH == 1: the two accumulators alternate between generations (double buffer).
+        // MH == 2: one generation fills both, accumulator h holding M-half h.
         const uint32_t acc = MH == 2 ? 0u : (lt & 1u);
         const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const uint32_t kb_end = (kGenerations && kb0 + p.k_gen < k_blocks) ? kb0 + p.k_gen : k_blocks;
+        for (uint32_t kb = kb0; kb < kb_end; ++kb) {
 #ifdef HODU_TC_PROFILE
           const long long tw = clock64();
 #endif
@@ -532,7 +549,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #endif
           if (!ok) break;
           tc_fence_after_sync();
-          if (kb == 0) {
+          if (kb == kb0) {
             // first write of the accumulator: the epilogue must have drained it
             PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
                                    code_base | 2u));
@@ -570,6 +587,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->tmem_full[acc + h]), 3);
           else umma_commit_1cta(smem_u32(&tail->tmem_full[acc + h]));
         }
+        ++lt;
+        kb0 = kb_end;
+      } while (kGenerations && kb0 < k_blocks);
       }
       PROF_DUMP(1);
 #ifdef HODU_TC_PROFILE
@@ -600,13 +620,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_empty0 =
         PAIR ? mapa_shared(smem_u32(&tail->tmem_empty[0]), 0u) : smem_u32(&tail->tmem_empty[0]);
     uint32_t lt = 0;
-    for (uint32_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt) {
+    bool epi_ok = true;
+    for (uint32_t t = first_tile; epi_ok && t < p.num_tiles; t += tile_step) {
+    uint32_t kb0 = 0;
+    do {   // one pass per accumulator generation (a single pass unless kGenerations)
+      const bool later_gen = kGenerations && kb0 != 0;   // add this generation's sums to the stored ones
       const uint32_t acc = MH == 2 ? half : (lt & 1u);
       const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
       bool ok = wait_bounded(smem_u32(&tail->tmem_full[acc]), acc_ph, abort_flag, p.status,
                              code_base | 4u);
       ok = __all_sync(0xFFFFFFFFu, ok);
-      if (!ok) break;
+      if (!ok) { epi_ok = false; break; }
       tc_fence_after_sync();
 #ifdef HODU_TC_PROFILE
       const long long epi_t0 = clock64();
@@ -648,7 +672,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
             }
             if constexpr (OUT == OUT_F32 || OUT == OUT_BF16 || OUT == OUT_F16) {
-              if (p.bias != nullptr) {  // uniform over the grid
+              if (p.bias != nullptr && !later_gen) {  // uniform over the grid; once per output
                 // Lane l fetches the bias of column c*32 + l; the 32 values go round by shuffle.
                 const uint32_t bcol = n0 + c * 32u + lane;
                 const float mine = bcol < p.N ? load_bias<OUT>(p.bias, static_cast<long long>(bcol) * p.bias_stride) : 0.0f;
@@ -739,7 +763,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               uint32_t pk[ChunkWords<OUT>::value];
               pack_chunk<OUT>(v, pk);
               store_packed_staged<ChunkWords<OUT>::value>(out_tile, p.ldc * osz, row - lane, p.M, col * osz,
-                                                          p.N * osz, pk, stage_buf, lane);
+                                                          p.N * osz, pk, stage_buf, lane,
+                                                          OUT == OUT_F32 && later_gen);
             }
           } else if (row_ok) {
             const int ncols = static_cast<int>(min(32u, p.N - col));
@@ -748,21 +773,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
-      if (released) {
-#ifdef HODU_TC_PROFILE
-        if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2 + 1] += clock64() - epi_t0;
-#endif
-        continue;
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (PAIR) mbar_arrive_cluster_addr(tmem_empty0 + acc * 8u);
-        else mbar_arrive(tmem_empty0 + acc * 8u);
+      if (!released) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster_addr(tmem_empty0 + acc * 8u);
+          else mbar_arrive(tmem_empty0 + acc * 8u);
+        }
       }
 #ifdef HODU_TC_PROFILE
       if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2 + 1] += clock64() - epi_t0;
 #endif
+      ++lt;
+      kb0 += p.k_gen;
+    } while (kGenerations && kb0 < p.k_blocks);
     }
   }
 
@@ -1214,6 +1238,14 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
 #ifdef HODU_TC_PROFILE
   if (const char* e = getenv("HODU_TC_EXPERIMENT")) p.out_vec_ok |= static_cast<uint32_t>(atoi(e)) & 14u;
 #endif
+  // The tensor core adds into its f32 accumulator with truncation, so the error of a long sum
+  // grows with its length (7e-5 of the largest output at K = 8192 with one accumulator per
+  // tile, against the 1e-4 bar of the f32 path).  Long f32 products therefore run as
+  // generations of 64 k-blocks (2048 elements of K; 32 beyond K = 32768): each generation starts a
+  // fresh accumulator and the epilogue adds it to the output in round-to-nearest f32.
+  p.k_gen = p.k_blocks;
+  if (kind == KIND_TF32 && pb.f32_presplit && (p.out_vec_ok & 1u) && !pb.swiglu && p.k_blocks > 128u)
+    p.k_gen = p.k_blocks > 3072u ? 32u : 64u;
 
   int device = 0;
   cudaGetDevice(&device);

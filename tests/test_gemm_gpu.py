@@ -326,3 +326,18 @@ def test_small_outputs_with_long_k_are_split_over_k(case):
     want = O.matmul(a_store, b_store, md, in_dt, out_dt, scales[0] * scales[1], is_dot=True)
     tol = {O.F32: 1e-4, O.BF16: 1e-2, O.F16: 1e-2}[out_dt] if in_dt != O.F8E4M3 else 6e-2
     check_close(got, want, out_dt, tol)
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 16384, 512), (512, 40000, 256), (1024, 8192, 1024)])
+def test_f32_long_k_stays_inside_the_bar(m, k, n):
+    """The tensor core adds into its f32 accumulator with truncation; one accumulator over a long
+    K drifts past the 1e-4 bar (2.8e-4 measured at K = 32768).  The f32 path restarts the
+    accumulator every 2048 (1024) elements of K and adds the generations in f32 on the way out."""
+    rng = np.random.default_rng(k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    md = dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n)))
+    got, taken = gpu_matmul(a, b, md, O.F32, O.F32, is_dot=True)
+    assert taken == K._lib.PATH_TENSOR
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32).reshape(-1)
+    assert O.rel_err(got, want) <= 2e-5
