@@ -118,3 +118,27 @@ def test_reference_cast_known_answers(case):
     got = d_out.cpu().numpy()[: want.size * want.itemsize].view(want.dtype)
     assert np.array_equal(got, want)
     assert not d_out.cpu().numpy()[want.size * want.itemsize:].any()   # nothing written past the end
+
+
+def test_cast_of_more_than_two_to_the_32_elements():
+    """Maximum sizes: 2^32 + 4096 contiguous f32 elements to bf16 (the reference's CUDA cast indexes
+    with uint32_t, crates/hodu_cuda_kernels/kernels/ops_cast.cu:7-30).  Slices at the start, around
+    the 2^32 boundary and at the very end must equal round-to-nearest-even bit for bit."""
+    import torch
+    n = (1 << 32) + 4096
+    dev = torch.device("cuda:0")
+    src = torch.empty(n, dtype=torch.float32, device=dev)
+    step = 1 << 28
+    g = torch.Generator(device=dev).manual_seed(3)
+    for lo in range(0, n, step):                     # filled in pieces: no 17 GB temporary
+        hi = min(n, lo + step)
+        src[lo:hi].normal_(generator=g)
+    out = torch.zeros(n + 64, dtype=torch.int16, device=dev)
+    K.call_ops_cast(K.cast.F32_BF16, 0, src.data_ptr(), out.data_ptr(), cast_metadata(Layout.from_shape((n,))), 0)
+    assert K.last_status(0) == 0
+    for lo, hi in ((0, 4096), ((1 << 31) - 2048, (1 << 31) + 2048), ((1 << 32) - 2048, (1 << 32) + 2048), (n - 4096, n)):
+        want = src[lo:hi].to(torch.bfloat16).view(torch.int16)
+        assert torch.equal(out[lo:hi], want), (lo, hi)
+    assert not bool(out[n:].any().item())            # nothing written past the end
+    del src, out
+    torch.cuda.empty_cache()

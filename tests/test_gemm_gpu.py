@@ -341,3 +341,30 @@ def test_f32_long_k_stays_inside_the_bar(m, k, n):
     assert taken == K._lib.PATH_TENSOR
     want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32).reshape(-1)
     assert O.rel_err(got, want) <= 2e-5
+
+
+def test_output_beyond_two_to_the_31_elements():
+    """Maximum sizes: an output of 66000 x 33000 = 2.18e9 elements (4.4 GB of bf16), so element
+    and byte offsets pass 2^31 and 2^32; rows sampled from both ends and the middle are checked
+    against the oracle, and the element after the last one is untouched."""
+    import torch
+    m, k, n = 66000, 32, 33000
+    rng = np.random.default_rng(7)
+    a = O.narrow(rng.standard_normal((m, k)).astype(np.float32), O.BF16)
+    b = O.narrow(rng.standard_normal((k, n)).astype(np.float32), O.BF16)
+    md = dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n)))
+    dev = torch.device("cuda:0")
+    ta = torch.from_numpy(a.view(np.int16)).to(dev)
+    tb = torch.from_numpy(b.view(np.int16)).to(dev)
+    out = torch.empty(m * n + 64, dtype=torch.int16, device=dev)
+    out[m * n:] = 0x5A5A
+    K.call_ops_dot(K.dot.BF16, 0, ta.data_ptr(), tb.data_ptr(), out.data_ptr(), md, 0)
+    assert K.last_status(0) == 0 and K.last_path() == K._lib.PATH_TENSOR
+    assert bool((out[m * n:] == 0x5A5A).all().item())
+    af, bf = O.widen(a, O.BF16).reshape(m, k), O.widen(b, O.BF16).reshape(k, n)
+    for r in (0, 1, 32767, 32768, 65535, 65536, m - 1):
+        got = out[r * n:(r + 1) * n].cpu().numpy().view(np.uint16)
+        want = O.narrow(af[r:r + 1] @ bf, O.BF16).reshape(-1)
+        assert O.rel_err(O.widen(got, O.BF16), O.widen(want, O.BF16)) <= 1e-2, r
+    del out
+    torch.cuda.empty_cache()
