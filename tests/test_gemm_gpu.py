@@ -368,3 +368,37 @@ def test_output_beyond_two_to_the_31_elements():
         assert O.rel_err(O.widen(got, O.BF16), O.widen(want, O.BF16)) <= 1e-2, r
     del out
     torch.cuda.empty_cache()
+
+
+def test_empty_extents_on_every_entry_point():
+    """Empty inputs: every entry point returns success, launches nothing and leaves the output alone."""
+    import torch
+    from hodu_b200.einsum import ParsedEinsum, einsum_metadata
+    from hodu_b200.op_metadatas import cast_metadata, conv2d_metadata, swiglu_metadata
+    dev = torch.device("cuda:0")
+    buf = torch.full((256,), 7, dtype=torch.int16, device=dev)
+    p = buf.data_ptr()
+    before = K.launch_count()
+    for (m, k, n) in ((0, 8, 8), (8, 8, 0), (0, 0, 0)):
+        K.call_ops_dot(K.dot.BF16, 0, p, p, p, dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n))), 0)
+        K.call_ops_matmul_ex(DType.I8, DType.I32, 0, p, p, p,
+                             dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n))), is_dot=True)
+    for bshape in ((0, 4, 4), (3, 0, 4)):
+        la = Layout.from_shape(bshape)
+        lb = Layout.from_shape((bshape[0], bshape[2], 5))
+        K.call_ops_matmul(K.matmul.F16, 0, p, p, p, matmul_metadata(la, lb, Layout.from_shape((bshape[0], bshape[1], 5))), 0)
+    K.call_ops_cast(K.cast.F32_BF16, 0, p, p, cast_metadata(Layout.from_shape((0,))), 0)
+    K.call_ops_contiguous(K.contiguous.BF16, 0, p, p, cast_metadata(Layout.from_shape((4, 0))), 0)
+    K.call_ops_swiglu(DType.BF16, 0, p, p, p, p,
+                      swiglu_metadata(Layout.from_shape((0, 8)), Layout.from_shape((8, 16)), Layout.from_shape((8, 16))))
+    K.call_ops_linear(DType.BF16, 0, p, p, p, p,
+                      [*matmul_metadata(Layout.from_shape((0, 8)), Layout.from_shape((8, 4)), Layout.from_shape((0, 4))), 1, 0])
+    shapes = [(0, 3), (3, 4)]
+    parsed = ParsedEinsum.parse("ij,jk->ik", shapes)
+    K.call_ops_einsum(K.einsum.BF16, 0, [p, p], p,
+                      einsum_metadata(parsed, [Layout.from_shape(s) for s in shapes], Layout.from_shape((0, 4))), 0)
+    K.call_ops_conv(K.conv2d.BF16, 0, p, p, p, conv2d_metadata(0, 3, 4, (5, 5), (3, 3)), 0)
+    torch.cuda.synchronize()
+    assert K.launch_count() == before
+    assert K.last_status(0) == 0
+    assert bool((buf == 7).all().item())
