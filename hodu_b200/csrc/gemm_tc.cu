@@ -90,6 +90,7 @@ struct TcParams {
   uint32_t M, N, K;
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks, group_m;
   uint32_t k_gen;         // k-blocks per accumulator generation (== k_blocks: one generation per tile)
+  uint32_t k_gen_limit;   // generations of k_gen blocks up to here, then ONE generation for the rest
   uint32_t bdim1, bdim2;  // batch = (b0 * bdim1 + b1) * bdim2 + b2
   uint32_t bk;            // K elements per stage (128 bytes worth)
   OperandLoad a, b;
@@ -168,6 +169,13 @@ __device__ __forceinline__ TileCoord decode_tile(const TcParams& p, uint32_t t) 
   c.mt = first_m + rr % gm;
   c.nt = rr / gm;
   return c;
+}
+
+// End (exclusive) of the accumulator generation that starts at k-block kb0.
+__device__ __forceinline__ uint32_t generation_end(const TcParams& p, uint32_t kb0) {
+  if (kb0 >= p.k_gen_limit) return p.k_blocks;
+  const uint32_t e = kb0 + p.k_gen;
+  return e < p.k_gen_limit ? e : p.k_gen_limit;
 }
 
 // -------------------------------------------------------------- epilogue helpers
@@ -538,7 +546,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t acc = MH == 2 ? 0u : (lt & 1u);
         const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const uint32_t kb_end = (kGenerations && kb0 + p.k_gen < k_blocks) ? kb0 + p.k_gen : k_blocks;
+        const uint32_t kb_end = kGenerations ? generation_end(p, kb0) : k_blocks;
         for (uint32_t kb = kb0; kb < kb_end; ++kb) {
 #ifdef HODU_TC_PROFILE
           const long long tw = clock64();
@@ -785,7 +793,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2 + 1] += clock64() - epi_t0;
 #endif
       ++lt;
-      kb0 += p.k_gen;
+      kb0 = generation_end(p, kb0);
     } while (kGenerations && kb0 < p.k_blocks);
     }
   }
@@ -1244,7 +1252,11 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   // generations of 128 k-blocks (4096 elements of K; 64 beyond K = 32768: 1e-5 measured
   // at every K up to 65536, for 12 % of the throughput): each generation starts a
   // fresh accumulator and the epilogue adds it to the output in round-to-nearest f32.
+  // (Generations over the hi x hi third of K' only, with the two small thirds as one last
+  // generation, measured 5 % faster but is wrong for K slices of a split product, which do not
+  // line up with the thirds; the limit below therefore stays at the whole K'.)
   p.k_gen = p.k_blocks;
+  p.k_gen_limit = p.k_blocks;
   if (kind == KIND_TF32 && pb.f32_presplit && (p.out_vec_ok & 1u) && !pb.swiglu && p.k_blocks > 128u)
     p.k_gen = p.k_blocks > 3072u ? 64u : 128u;
 
