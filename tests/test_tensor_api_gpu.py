@@ -213,3 +213,32 @@ def test_concurrent_calls_from_several_threads_on_one_device():
         t.join()
     assert not errors, errors
     assert K.last_status(0) == 0
+
+
+def test_shutdown_releases_everything_and_the_next_call_sets_up_again():
+    """`hodu_b200_shutdown` frees the status word, the scratch pool, the host-pipeline staging and
+    streams; the next call on the device initialises them again and computes the same result."""
+    lib = _lib.lib()
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((300, 1024)).astype(np.float32)     # f32: goes through the scratch pool
+    b = rng.standard_normal((1024, 200)).astype(np.float32)
+    md = dot_metadata(Layout.from_shape(a.shape), Layout.from_shape(b.shape))
+    ta, tb = to_dev(a), to_dev(b)
+    out1 = torch.empty(300 * 200, dtype=torch.float32, device=DEV)
+    K.call_ops_dot(K.dot.F32, 0, ta.data_ptr(), tb.data_ptr(), out1.data_ptr(), md, 0)
+    pa = torch.from_numpy(a.reshape(-1).copy()).pin_memory()
+    pb = torch.from_numpy(b.reshape(-1).copy()).pin_memory()
+    po = torch.empty(300 * 200, dtype=torch.float32).pin_memory()
+    K.call_ops_matmul_host(DType.F32, DType.F32, 0, pa.data_ptr(), pb.data_ptr(), po.data_ptr(), md, is_dot=True)
+    assert K.last_status(0) == 0
+    free_before = torch.cuda.mem_get_info(0)[0]
+    lib.hodu_b200_shutdown(0)
+    lib.hodu_b200_shutdown(0)                                   # idempotent
+    assert torch.cuda.mem_get_info(0)[0] >= free_before         # nothing was kept
+    assert lib.hodu_b200_init(0) == 0
+    out2 = torch.empty(300 * 200, dtype=torch.float32, device=DEV)
+    K.call_ops_dot(K.dot.F32, 0, ta.data_ptr(), tb.data_ptr(), out2.data_ptr(), md, 0)
+    K.call_ops_matmul_host(DType.F32, DType.F32, 0, pa.data_ptr(), pb.data_ptr(), po.data_ptr(), md, is_dot=True)
+    assert K.last_status(0) == 0
+    assert torch.equal(out1, out2)
+    assert O.rel_err(po.numpy(), O.matmul(a, b, md, O.F32, is_dot=True)) <= 1e-4
