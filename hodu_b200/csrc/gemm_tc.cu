@@ -630,6 +630,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t lt = 0;
     bool epi_ok = true;
     for (uint32_t t = first_tile; epi_ok && t < p.num_tiles; t += tile_step) {
+    // Where this tile's rows go: worked out BEFORE the wait for the accumulator (these divisions
+    // and 64-bit products measured ~800 cycles, which were exposed after the wait).
+    const TileCoord tc = decode_tile(p, t);
+    const uint32_t row = tc.mt * kTileM + rank * 128u * MH + half * 128u + q * 32u + lane;
+    const uint32_t n0 = tc.nt * kOutCols;
+    const bool row_ok = row < p.M;
+    uint8_t* out_row = static_cast<uint8_t*>(p.out) +
+                       (static_cast<unsigned long long>(tc.batch) * p.out_batch_stride +
+                        static_cast<unsigned long long>(row) * p.ldc + n0) * osz;
+    uint8_t* out_tile = static_cast<uint8_t*>(p.out) +
+                        static_cast<unsigned long long>(tc.batch) * p.out_batch_stride * osz;
     uint32_t kb0 = 0;
     do {   // one pass per accumulator generation (a single pass unless kGenerations)
       const bool later_gen = kGenerations && kb0 != 0;   // add this generation's sums to the stored ones
@@ -643,13 +654,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #ifdef HODU_TC_PROFILE
       const long long epi_t0 = clock64();
 #endif
-      const TileCoord tc = decode_tile(p, t);
-      const uint32_t row = tc.mt * kTileM + rank * 128u * MH + half * 128u + q * 32u + lane;
-      const uint32_t n0 = tc.nt * kOutCols;
-      const bool row_ok = row < p.M;
-      uint8_t* out_row = static_cast<uint8_t*>(p.out) +
-                         (static_cast<unsigned long long>(tc.batch) * p.out_batch_stride +
-                          static_cast<unsigned long long>(row) * p.ldc + n0) * osz;
       const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
       // Loads chunk c of this warp's rows from TMEM and applies the epilogue arithmetic; v then
       // holds the 32 final values (floats, or raw s32).
@@ -696,8 +700,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       };
-      uint8_t* out_tile = static_cast<uint8_t*>(p.out) +
-                          static_cast<unsigned long long>(tc.batch) * p.out_batch_stride * osz;
       const bool staged = kStaged && (p.out_vec_ok & 1u);  // uniform over the warp
       // The 512x256 form cannot hide its epilogue behind the next tile, so for 2-byte outputs
       // the warp first pulls ALL its chunks out of TMEM into registers (already packed), hands
