@@ -139,6 +139,8 @@ def cpu_reference_rate(workload: str, budget_s: float):
     ref = O.ref()
     have_blas = ref is not None and ref.blas is not None
     kind = "reference" if have_blas else "port"
+    if have_blas:   # all host cores, whatever OMP_NUM_THREADS the launcher exported
+        ref.set_blas_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = ref.blas_info()["threads"] if have_blas else (os.cpu_count() or 1)
 
     def run(a, b, md, is_dot):

@@ -82,6 +82,21 @@ class _Ref:
         ptrs = (C_.c_void_p * len(inputs))(*[a.ctypes.data for a in inputs])
         fn(ptrs, _ptr(out), _md(md))
 
+    def set_blas_threads(self, n: int) -> int:
+        """openblas_set_num_threads(n) on the OpenBLAS behind hodu_cpu_{matmul,dot}_f32 (launchers
+        such as torchrun export OMP_NUM_THREADS=1, which OpenBLAS would otherwise obey).
+        Returns the thread count in effect afterwards (0 if there is no BLAS build)."""
+        note = os.path.join(HERE, "_ref", "blas.txt")
+        if self.blas is None or not os.path.exists(note):
+            return 0
+        path, prefix = [l.strip() for l in open(note).read().split("\n")[:2]]
+        try:
+            ob = C_.CDLL(path)
+            getattr(ob, prefix + "openblas_set_num_threads")(C_.c_int(int(n)))
+            return int(getattr(ob, prefix + "openblas_get_num_threads")())
+        except (OSError, AttributeError):
+            return 0
+
     def blas_info(self) -> dict:
         """Thread count and build string of the OpenBLAS behind hodu_cpu_{matmul,dot}_f32."""
         info = {"threads": 0, "config": "none", "path": ""}
