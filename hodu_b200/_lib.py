@@ -30,7 +30,9 @@ SIGNATURES = {
     "hodu_b200_conv2d": (_i, [_i, _vp, _u8, _vp, _vp, _vp, _szp, _sz]),
     "hodu_b200_matmul_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
     "hodu_b200_dot_host": (_i, [_i, _u8, _u8, _vp, _vp, _vp, _szp, _sz, _f, _f]),
+    "hodu_b200_swiglu_mlp_host": (_i, [_i, _u8, _vp, _vp, _vp, _vp, _vp, _szp, _sz, _u32]),
     "hodu_b200_dot_f32_static": (_i, [_i, _vp, _vp, _vp, _vp, _szp, _sz]),
+    "hodu_b200_dot_f32_static_status": (_i, [_i, C.POINTER(C.c_uint32)]),
     "hodu_b200_strerror": (C.c_char_p, [_i]),
     "hodu_b200_last_error_message": (C.c_char_p, []),
     "hodu_b200_last_status": (_i, [_i, C.POINTER(C.c_uint32)]),

@@ -21,6 +21,9 @@ std::atomic<int> g_forced_path{HODU_B200_PATH_AUTO};
 std::atomic<unsigned long long> g_launches{0};
 std::mutex g_state_mu;
 DeviceState g_state[kMaxDevices];
+// Published with release order once every field of g_state[d] is written; readers that see it
+// set (acquire) may use the state without taking the lock.
+std::atomic<bool> g_state_ready[kMaxDevices];
 
 // Tensor-core path only above this much work; below it one CUDA-core CTA wave
 // finishes sooner than the TMA/TMEM pipeline fills.
@@ -74,9 +77,9 @@ DeviceState* device_state(int device) {
     return nullptr;
   }
   DeviceState* st = &g_state[device];
-  if (st->ready) return st;
+  if (g_state_ready[device].load(std::memory_order_acquire)) return st;
   std::lock_guard<std::mutex> lock(g_state_mu);
-  if (st->ready) return st;
+  if (g_state_ready[device].load(std::memory_order_relaxed)) return st;
   DeviceGuard guard(device);
   if (!guard.ok) {
     fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
@@ -99,11 +102,15 @@ DeviceState* device_state(int device) {
     return nullptr;
   }
   st->ready = true;
+  g_state_ready[device].store(true, std::memory_order_release);
   return st;
 }
 
 int scratch_alloc(DeviceState* st, void** ptr, size_t bytes, cudaStream_t stream) {
-  if (!st->pool) {
+  cudaMemPool_t pool_now = nullptr;
+  {
+    // The pool pointer is read and created under the lock (an allocation follows anyway, so the
+    // lock costs nothing that matters).
     std::lock_guard<std::mutex> lock(g_state_mu);
     if (!st->pool) {
       cudaMemPoolProps props = {};
@@ -117,8 +124,9 @@ int scratch_alloc(DeviceState* st, void** ptr, size_t bytes, cudaStream_t stream
       HODU_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep), HODU_B200_ERR_MEMORY);
       st->pool = pool;
     }
+    pool_now = st->pool;
   }
-  HODU_CUDA_TRY(cudaMallocFromPoolAsync(ptr, bytes, st->pool, stream), HODU_B200_ERR_MEMORY);
+  HODU_CUDA_TRY(cudaMallocFromPoolAsync(ptr, bytes, pool_now, stream), HODU_B200_ERR_MEMORY);
   return 0;
 }
 
@@ -145,6 +153,56 @@ bool in_out_pair_ok(int in, int out) {
 }
 bool is_int_dtype(int dt) { return dt == HODU_DTYPE_I8 || dt == HODU_DTYPE_I32; }
 }  // namespace
+
+namespace {
+constexpr unsigned long long kMaxExtent = 1ull << 32;
+constexpr unsigned long long kMaxSpan = 1ull << 48;
+
+// Elements between the first and the last element an operand view touches, or ~0 if any of its
+// numbers is out of range.  128-bit arithmetic: the inputs are arbitrary 64-bit words.
+unsigned long long operand_span(const Operand& op, int64_t rows, int64_t cols, const Problem& pb) {
+  unsigned __int128 span = 0;
+  auto add = [&](int64_t extent, int64_t stride) {
+    if (extent < 0 || static_cast<unsigned long long>(extent) > kMaxExtent || stride < 0 ||
+        static_cast<unsigned long long>(stride) > kMaxSpan)
+      return false;
+    if (extent > 1) span += static_cast<unsigned __int128>(extent - 1) * static_cast<unsigned long long>(stride);
+    return span <= kMaxSpan;
+  };
+  if (op.offset < 0 || static_cast<unsigned long long>(op.offset) > kMaxSpan) return ~0ull;
+  span = static_cast<unsigned long long>(op.offset);
+  if (!add(rows, op.stride_r) || !add(cols, op.stride_c)) return ~0ull;
+  for (int d = 0; d < pb.batch_ndim; ++d)
+    if (!add(pb.batch_shape[d], op.bstride[d])) return ~0ull;
+  return static_cast<unsigned long long>(span);
+}
+}  // namespace
+
+int check_extents(const Problem& pb) {
+  const char* what = nullptr;
+  if (pb.batch_ndim < 0 || pb.batch_ndim > 16) what = "batch rank";
+  unsigned __int128 out_elems = 1, batches = 1;
+  for (int d = 0; !what && d < pb.batch_ndim; ++d) {
+    if (pb.batch_shape[d] < 0 || static_cast<unsigned long long>(pb.batch_shape[d]) > kMaxExtent) what = "batch extent";
+    else batches *= static_cast<unsigned long long>(pb.batch_shape[d]);
+    if (batches > kMaxSpan) what = "batch count";
+  }
+  if (!what && (pb.M < 0 || pb.N < 0 || pb.K < 0 || static_cast<unsigned long long>(pb.M) > kMaxExtent ||
+                static_cast<unsigned long long>(pb.N) > kMaxExtent || static_cast<unsigned long long>(pb.K) > kMaxExtent))
+    what = "M, N or K";
+  if (!what) {
+    out_elems = batches * static_cast<unsigned long long>(pb.M) * static_cast<unsigned long long>(pb.N);
+    const unsigned __int128 a_elems = static_cast<unsigned __int128>(pb.M) * static_cast<unsigned long long>(pb.K);
+    const unsigned __int128 b_elems = static_cast<unsigned __int128>(pb.K) * static_cast<unsigned long long>(pb.N);
+    if (out_elems > kMaxSpan || a_elems > kMaxSpan || b_elems > kMaxSpan) what = "element count";
+  }
+  if (!what && operand_span(pb.a, pb.M, pb.K, pb) == ~0ull) what = "lhs strides or offset";
+  if (!what && operand_span(pb.b, pb.K, pb.N, pb) == ~0ull) what = "rhs strides or offset";
+  if (!what && pb.swiglu && operand_span(pb.b2, pb.K, pb.N, pb) == ~0ull) what = "second rhs strides or offset";
+  if (what)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "%s out of range (extents up to 2^32, strides, offsets and element counts up to 2^48)", what);
+  return 0;
+}
 
 // [num_els, lhs_ndim, rhs_ndim, batch_ndim, lhs_shape.., rhs_shape.., batch_shape..,
 //  lhs_strides.., rhs_strides.., lhs_off, rhs_off, M, K, N]
@@ -173,11 +231,15 @@ int parse_matmul(const size_t* md, size_t len, Problem* pb) {
   pb->batch_ndim = static_cast<int>(bn);
   pb->batches = 1;
   for (size_t d = 0; d < bn; ++d) {
+    if (bshape[d] > kMaxExtent || static_cast<unsigned __int128>(pb->batches) * bshape[d] > kMaxSpan)
+      return fail(HODU_B200_ERR_INVALID_INPUT, "matmul: batch extents out of range");
     pb->batch_shape[d] = static_cast<int64_t>(bshape[d]);
     pb->batches *= static_cast<int64_t>(bshape[d]);
     pb->a.bstride[d] = 0;
     pb->b.bstride[d] = 0;
   }
+  if (M > kMaxExtent || N > kMaxExtent || K > kMaxExtent)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "matmul: M, N or K out of range");
   for (size_t d = 0; d + 2 < ln; ++d) {
     const size_t od = bn - (ln - 2) + d;
     if (lshape[d] != 1 && lshape[d] != bshape[od])
@@ -190,7 +252,7 @@ int parse_matmul(const size_t* md, size_t len, Problem* pb) {
       return fail(HODU_B200_ERR_INVALID_INPUT, "matmul: rhs batch dim %zu (%zu) does not broadcast to %zu", d, rshape[d], bshape[od]);
     pb->b.bstride[od] = rshape[d] == 1 ? 0 : static_cast<int64_t>(rstr[d]);
   }
-  if (num_els != static_cast<size_t>(pb->batches) * M * N)
+  if (static_cast<unsigned __int128>(num_els) != static_cast<unsigned __int128>(pb->batches) * M * N)
     return fail(HODU_B200_ERR_INVALID_INPUT, "matmul: num_els %zu != batches*M*N", num_els);
   pb->a.offset = static_cast<int64_t>(loff);
   pb->b.offset = static_cast<int64_t>(roff);
@@ -198,7 +260,7 @@ int parse_matmul(const size_t* md, size_t len, Problem* pb) {
   pb->a.stride_c = static_cast<int64_t>(lstr[ln - 1]);
   pb->b.stride_r = static_cast<int64_t>(rstr[rn - 2]);
   pb->b.stride_c = static_cast<int64_t>(rstr[rn - 1]);
-  return 0;
+  return check_extents(*pb);
 }
 
 // [M, K, N, lhs_stride_m, lhs_stride_k, rhs_stride_k, rhs_stride_n, lhs_off, rhs_off]
@@ -211,7 +273,7 @@ int parse_dot(const size_t* md, size_t len, Problem* pb) {
   pb->a.offset = md[7]; pb->b.offset = md[8];
   pb->batch_ndim = 0;
   pb->batches = 1;
-  return 0;
+  return check_extents(*pb);
 }
 
 namespace {
@@ -300,7 +362,8 @@ void hodu_b200_shutdown(int device) {
   if (device < 0 || device >= kMaxDevices) return;
   std::lock_guard<std::mutex> lock(g_state_mu);
   DeviceState* st = &g_state[device];
-  if (!st->ready) return;
+  if (!g_state_ready[device].load(std::memory_order_relaxed)) return;
+  g_state_ready[device].store(false, std::memory_order_release);
   DeviceGuard guard(device);
   if (guard.ok) {
     cudaDeviceSynchronize();
@@ -355,6 +418,8 @@ int hodu_b200_swiglu(int device, void* stream, uint8_t dtype, const void* x, con
   pb.b2.stride_r = md[7]; pb.b2.stride_c = md[8];
   pb.a.offset = md[9]; pb.b.offset = md[10]; pb.b2.offset = md[11];
   pb.batch_ndim = 0; pb.batches = 1;
+  pb.swiglu = true;
+  if (const int rc = check_extents(pb)) return rc;
   if (pb.M == 0 || pb.N == 0) return 0;
   if (!out) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
   DeviceState* st = device_state(device);
@@ -388,6 +453,8 @@ int hodu_b200_linear(int device, void* stream, uint8_t dtype, const void* x, con
   pb.in_dtype = dtype; pb.out_dtype = dtype;
   pb.a.ptr = x; pb.b.ptr = w; pb.out = out;
   pb.bias = bias;
+  if (md[len - 2] > kMaxSpan || md[len - 1] > kMaxSpan)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "linear: bias stride or offset out of range");
   pb.bias_stride = static_cast<int64_t>(md[len - 2]);
   pb.bias_offset = static_cast<int64_t>(md[len - 1]);
   pb.bias_flags = flags;

@@ -130,7 +130,7 @@ int launch_cast(int src, int dst, const void* in, void* out, const size_t* md, s
                 int device, cudaStream_t stream) {
   if (!md || md_len < 3) return fail(HODU_B200_ERR_INVALID_INPUT, "cast: metadata too short");
   const size_t n = md[0], ndim = md[1];
-  if (md_len != 3 + 2 * ndim)
+  if (ndim > 64 || md_len != 3 + 2 * ndim)   // the bound first: 2 * ndim wraps for ndim >= 2^63
     return fail(HODU_B200_ERR_INVALID_INPUT, "cast: metadata length %zu does not match ndim %zu", md_len, ndim);
   const size_t* shape = md + 2;
   const size_t* strides = md + 2 + ndim;

@@ -120,6 +120,11 @@ int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t strea
                           size_t scratch_bytes, const char** why);
 // One tiny kernel whose only wait can never be satisfied; it gives up after limit_ms.
 int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t limit_ms);
+// Refuses problems whose extents, strides or offsets are beyond anything a real buffer can hold
+// (extent > 2^32, stride or offset > 2^48, an operand that spans more than 2^48 elements, more
+// than 2^48 output elements), so that the host arithmetic further down -- products of extents,
+// strides times extents, byte sizes -- cannot overflow.  Every parser ends with it.
+int check_extents(const Problem& pb);
 // Parsers of the reference's wire formats and the path chooser (api.cu).
 int parse_matmul(const size_t* md, size_t len, Problem* pb);
 int parse_dot(const size_t* md, size_t len, Problem* pb);

@@ -43,7 +43,7 @@ bool merge_stride(const EinsumInput& in, const int* ids, int n, const size_t* si
       inner_extent = static_cast<int64_t>(sz);
       have = true;
     } else {
-      if (s != inner_stride * inner_extent) return false;
+      if (static_cast<__int128>(s) != static_cast<__int128>(inner_stride) * inner_extent) return false;
       inner_extent *= static_cast<int64_t>(sz);
     }
   }
@@ -93,6 +93,19 @@ int parse_einsum(const size_t* md, size_t len, size_t num_inputs, Problem* pb, b
   pos += n_idx;
   const size_t* out_ids = md + pos;
 
+  {  // index sizes a real tensor can have: each up to 2^32, all together up to 2^48 elements
+    unsigned __int128 total = 1;
+    for (size_t x = 0; x < n_idx; ++x) {
+      if (sizes[x] > (1ull << 32)) return fail(HODU_B200_ERR_INVALID_INPUT, "einsum: index size %zu out of range", sizes[x]);
+      if (sizes[x] > 0) total *= sizes[x];
+      if (total > (1ull << 48)) return fail(HODU_B200_ERR_INVALID_INPUT, "einsum: index sizes multiply to more than 2^48");
+    }
+    for (int i = 0; i < 2; ++i) {
+      if (in[i].offset > (1ull << 48)) return fail(HODU_B200_ERR_INVALID_INPUT, "einsum: offset out of range");
+      for (size_t dd = 0; dd < in[i].ndim; ++dd)
+        if (in[i].stride[dd] > (1ull << 48)) return fail(HODU_B200_ERR_INVALID_INPUT, "einsum: stride out of range");
+    }
+  }
   int out_dim_of_index[kMaxIdx];
   for (size_t x = 0; x < n_idx; ++x) out_dim_of_index[x] = -1;
   size_t expect_out = 1;
@@ -184,7 +197,7 @@ int parse_einsum(const size_t* md, size_t len, size_t num_inputs, Problem* pb, b
   pb->b.stride_r = b_sr; pb->b.stride_c = b_sc;
   pb->a.offset = static_cast<int64_t>(A.offset);
   pb->b.offset = static_cast<int64_t>(B.offset);
-  return 0;
+  return check_extents(*pb);
 }
 
 }  // namespace hodu_b200

@@ -82,6 +82,9 @@ __device__ __forceinline__ void split_tf32_body(const SplitParams& p, unsigned b
 // Both operands of one product in one launch: the first `blocks_a` CTAs split the lhs, the
 // rest the rhs.
 __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitParams pa, const SplitParams pb, unsigned blocks_a) {
+  // The product kernel that follows waits for this grid before it reads the split operands
+  // (griddepcontrol.wait); letting it launch now overlaps its set-up with this pass.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (blockIdx.x < blocks_a) split_tf32_body(pa, blockIdx.x, blocks_a);
   else split_tf32_body(pb, blockIdx.x - blocks_a, gridDim.x - blocks_a);
 }
@@ -117,6 +120,7 @@ bool plan_split(const Problem& pb, const Operand& op, bool is_lhs, SplitPlan* pl
   for (int j = n - 1; j >= 0; --j) {
     const int d = dims[j];
     plan->out.bstride[d] = dense;
+    if (static_cast<__int128>(dense) * pb.batch_shape[d] > (static_cast<__int128>(1) << 50)) return false;  // no such scratch exists
     dense *= pb.batch_shape[d];
   }
   for (int j = 0; j < n; ++j) {
@@ -276,4 +280,26 @@ extern "C" int hodu_b200_dot_f32_static(int device, void* stream, const void* lh
   if (r == 1) return fail(HODU_B200_ERR_INVALID_INPUT, "dot_f32_static refused: %s", why);
   if (r == 0) set_last_path(HODU_B200_PATH_TENSOR);
   return r;
+}
+
+// Reads (and clears) the status word private to the entry point above.  Allocates nothing and
+// does not touch the library's per-device state: it synchronises the device, copies four bytes
+// from the address static_setup resolved, and clears the word if it was set.
+extern "C" int hodu_b200_dot_f32_static_status(int device, uint32_t* device_status_word) {
+  using namespace hodu_b200;
+  if (device < 0 || device >= kMaxDevices)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "device %d out of range 0..%d", device, kMaxDevices - 1);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+  StaticSetup* ss = nullptr;
+  if (const int r = static_setup(device, &ss)) return r;
+  HODU_CUDA_TRY(cudaDeviceSynchronize(), HODU_B200_ERR_LAUNCH);
+  uint32_t w = 0;
+  HODU_CUDA_TRY(cudaMemcpy(&w, ss->status, sizeof(w), cudaMemcpyDeviceToHost), HODU_B200_ERR_MEMORY);
+  if (w != 0) HODU_CUDA_TRY(cudaMemset(ss->status, 0, sizeof(w)), HODU_B200_ERR_MEMORY);
+  if (device_status_word) *device_status_word = w;
+  if (w != 0)
+    return fail(HODU_B200_ERR_DEVICE_STATUS, "static entry point: device status word 0x%08x (cta %u, wait %u)", w,
+                (w >> 4) & 0xFFFFu, w & 0xFu);
+  return 0;
 }

@@ -30,6 +30,7 @@ struct SimtParams {
   long long M, N, K;
   long long a_sr, a_sc, b_sr, b_sc, b2_sr, b2_sc;  // element strides (offset already applied)
   int batch_ndim;
+  long long batches;       // product of bshape[0..batch_ndim)
   long long bshape[16];
   long long a_bs[16], b_bs[16], b2_bs[16];
   float alpha;
@@ -73,8 +74,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
   __shared__ Acc B2s[SWIGLU ? TK : 1][TN + 4];
 
   const long long per_batch = p.tiles_m * p.tiles_n;
-  for (long long tile = blockIdx.x; tile < per_batch * p.bshape[15]; tile += gridDim.x) {
-    // p.bshape[15] carries the flattened batch count (slot unused by real dims).
+  for (long long tile = blockIdx.x; tile < per_batch * p.batches; tile += gridDim.x) {
     const long long batch = tile / per_batch;
     const long long r = tile - batch * per_batch;
     const long long m0 = (r / p.tiles_n) * TM;
@@ -197,7 +197,7 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream) {
   p.a_sr = pb.a.stride_r; p.a_sc = pb.a.stride_c;
   p.b_sr = pb.b.stride_r; p.b_sc = pb.b.stride_c;
   p.b2_sr = pb.b2.stride_r; p.b2_sc = pb.b2.stride_c;
-  if (pb.batch_ndim > 15) return fail(HODU_B200_ERR_INVALID_INPUT, "more than 15 batch dims");
+  if (pb.batch_ndim > 16) return fail(HODU_B200_ERR_INVALID_INPUT, "more than 16 batch dims");
   p.batch_ndim = pb.batch_ndim;
   for (int d = 0; d < pb.batch_ndim; ++d) {
     p.bshape[d] = pb.batch_shape[d];
@@ -205,7 +205,7 @@ int launch_gemm_simt(const Problem& pb, DeviceState* st, cudaStream_t stream) {
     p.b_bs[d] = pb.b.bstride[d];
     p.b2_bs[d] = pb.b2.bstride[d];
   }
-  p.bshape[15] = pb.batches;
+  p.batches = pb.batches;
   p.alpha = pb.alpha;
   p.swiglu_flags = pb.swiglu_flags;
   p.bias = pb.bias ? static_cast<const uint8_t*>(pb.bias) + pb.bias_offset * dtype_size(pb.out_dtype) : nullptr;

@@ -29,7 +29,9 @@
 
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -105,23 +107,6 @@ struct TcParams {
   void* out;
   uint32_t* status;
 };
-
-// Optional per-role wait accounting (compile with -DHODU_TC_PROFILE): cycles the roles of
-// CTA 0 and 1 spend inside their waits, read back with hodu_b200_debug_read_prof.
-#ifdef HODU_TC_PROFILE
-__device__ unsigned long long g_tc_prof[64];
-#define PROF_DECL long long prof_wait = 0, prof_t0 = clock64(), prof_tmp
-#define PROF_WAIT(expr) (prof_tmp = clock64(), ok = (expr), prof_wait += clock64() - prof_tmp, ok)
-#define PROF_DUMP(slot)                                                 \
-  if (blockIdx.x < 2) {                                                 \
-    g_tc_prof[(blockIdx.x * 4 + (slot)) * 2] = prof_wait;               \
-    g_tc_prof[(blockIdx.x * 4 + (slot)) * 2 + 1] = clock64() - prof_t0; \
-  }
-#else
-#define PROF_DECL
-#define PROF_WAIT(expr) (ok = (expr))
-#define PROF_DUMP(slot)
-#endif
 
 // -------------------------------------------------------------- bounded waits
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
@@ -378,7 +363,6 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
   const uint32_t full0 = PAIR ? mapa_shared(smem_u32(&tail->full[0]), 0u) : smem_u32(&tail->full[0]);
   uint32_t s = 0, ph = 0, issued = 0;
   bool ok = true;
-  PROF_DECL;
   for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step) {
     const TileCoord tc = decode_tile(p, t);
     const uint32_t b2 = tc.batch % p.bdim2;
@@ -393,17 +377,9 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
     else if (PAIR) mn0 = static_cast<int32_t>(SWIGLU ? tc.nt * 128u : tc.nt * 256u + rank * 128u);
     else mn0 = static_cast<int32_t>(tc.nt * kOutCols);
     for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-      PROF_WAIT(wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code));
+      ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code);
       if (!ok) break;
       const uint32_t bar = full0 + s * 8u;
-#ifdef HODU_TC_PROFILE
-      if (p.out_vec_ok & 2u) {  // experiment: no loads at all, the MMAs run on whatever is in smem
-        if (!PAIR || rank == 0) mbar_arrive(smem_u32(&tail->full[s]));
-        ++issued;
-        if (++s == kStages) { s = 0; ph ^= 1u; }
-        continue;
-      }
-#endif
       if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes);
       else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes);
       const int32_t k0 = static_cast<int32_t>(kb * p.bk);
@@ -424,7 +400,6 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
       if (++s == kStages) { s = 0; ph ^= 1u; }
     }
   }
-  PROF_DUMP(IS_A ? 0 : 3);
   if (*abort_flag && IS_A && rank == 0) {
     // Let copies already issued land before this CTA's shared memory goes away.  CTA 0's
     // `full` barriers count the bytes of both operands (and of both CTAs of a pair).
@@ -501,6 +476,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tail->tmem_base);
   const uint32_t code_base = 0x80000000u | ((blockIdx.x & 0xFFFFu) << 4);
+  // Everything above touched only this CTA's shared memory and TMEM, so under a programmatic
+  // dependent launch it ran while the previous kernel of the stream was finishing.  From here
+  // on global memory is read and written: wait for that kernel, then let the next one start
+  // its own set-up as soon as SMs free up.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer of A
@@ -521,10 +502,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0 && rank == 0) {
       uint32_t s = 0, ph = 0, lt = 0;
       bool ok = true;
-      PROF_DECL;
-#ifdef HODU_TC_PROFILE
-      long long prof_full = 0;
-#endif
       // This one thread's instruction stream bounds the main loop (with loads switched off the
       // kernel takes the same number of cycles), so the loop is kept to: one barrier wait, one
       // fence, one asm block of four MMAs per accumulator, one commit.  Everything else -- the
@@ -548,25 +525,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t d_tmem = tmem_base + acc * BN;
         const uint32_t kb_end = kGenerations ? generation_end(p, kb0) : k_blocks;
         for (uint32_t kb = kb0; kb < kb_end; ++kb) {
-#ifdef HODU_TC_PROFILE
-          const long long tw = clock64();
-#endif
           ok = wait_bounded(full_bar, ph, abort_flag, p.status, code_base | 3u);
-#ifdef HODU_TC_PROFILE
-          prof_full += clock64() - tw;
-#endif
           if (!ok) break;
           tc_fence_after_sync();
           if (kb == kb0) {
             // first write of the accumulator: the epilogue must have drained it
-            PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
-                                   code_base | 2u));
+            ok = wait_bounded(smem_u32(&tail->tmem_empty[acc]), acc_ph ^ 1u, abort_flag, p.status,
+                              code_base | 2u);
             if (!ok) break;
             tc_fence_after_sync();
             umma_x4<KIND, CG>(d_tmem, a_lo, a_hi, a_step, b_lo, b_hi, b_step, idesc, 0u);
             if constexpr (MH == 2) {
-              PROF_WAIT(wait_bounded(smem_u32(&tail->tmem_empty[1]), acc_ph ^ 1u, abort_flag, p.status,
-                                     code_base | 2u));
+              ok = wait_bounded(smem_u32(&tail->tmem_empty[1]), acc_ph ^ 1u, abort_flag, p.status,
+                                code_base | 2u);
               if (!ok) break;
               tc_fence_after_sync();
               umma_x4<KIND, CG>(d_tmem + BN, a_lo + (kHalfA >> 4), a_hi, a_step, b_lo, b_hi, b_step, idesc, 0u);
@@ -599,10 +570,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         kb0 = kb_end;
       } while (kGenerations && kb0 < k_blocks);
       }
-      PROF_DUMP(1);
-#ifdef HODU_TC_PROFILE
-      if (blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2] = prof_full;
-#endif
       if (*abort_flag) {
         if constexpr (PAIR) umma_commit_2cta(smem_u32(&tail->drain), 1);
         else umma_commit_1cta(smem_u32(&tail->drain));
@@ -651,9 +618,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) { epi_ok = false; break; }
       tc_fence_after_sync();
-#ifdef HODU_TC_PROFILE
-      const long long epi_t0 = clock64();
-#endif
       const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
       // Loads chunk c of this warp's rows from TMEM and applies the epilogue arithmetic; v then
       // holds the 32 final values (floats, or raw s32).
@@ -748,9 +712,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         }
-#ifdef HODU_TC_PROFILE
-        if (!(p.out_vec_ok & 8u))
-#endif
 #pragma unroll
         for (uint32_t i = 0; i < kChunks; ++i) {
           const uint32_t c = col_group * kChunks + i;
@@ -765,9 +726,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (col >= p.N) break;  // uniform over the warp
           uint32_t v[32];
           load_chunk(c, v);
-#ifdef HODU_TC_PROFILE
-          if (p.out_vec_ok & 8u) continue;  // experiment: no global stores
-#endif
           if (staged) {
             if constexpr (kStaged) {
               uint32_t pk[ChunkWords<OUT>::value];
@@ -778,6 +736,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           } else if (row_ok) {
             const int ncols = static_cast<int>(min(32u, p.N - col));
+            if constexpr (OUT == OUT_F32 && kGenerations) {
+              if (later_gen) {  // the lane that stored these elements adds the new generation to them
+                const float* old = reinterpret_cast<const float*>(out_row + static_cast<size_t>(c) * 32u * osz);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < ncols) v[j] = __float_as_uint(old[j] + __uint_as_float(v[j]));
+              }
+            }
             store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
                                  (p.out_vec_ok & 1u) != 0u);
           }
@@ -791,9 +757,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           else mbar_arrive(tmem_empty0 + acc * 8u);
         }
       }
-#ifdef HODU_TC_PROFILE
-      if (warp == 2 && lane == 0 && blockIdx.x < 2) g_tc_prof[(blockIdx.x * 4 + 2) * 2 + 1] += clock64() - epi_t0;
-#endif
       ++lt;
       kb0 = generation_end(p, kb0);
     } while (kGenerations && kb0 < p.k_blocks);
@@ -834,6 +797,12 @@ bool debug_enabled() {
   return on;
 }
 
+// HODU_B200_PDL=0 launches the tensor-core kernels without programmatic dependent launch.
+bool dependent_launch_enabled() {
+  static const bool on = [] { const char* e = getenv("HODU_B200_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -850,6 +819,45 @@ EncodeTiledFn encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   });
   return fn;
+}
+
+// Everything cuTensorMapEncodeTiled is given (swizzle, interleave, promotion and fill are fixed).
+struct MapKey {
+  uintptr_t base;
+  uint64_t dims[5];
+  uint64_t strides[4];
+  uint32_t box[5];
+  uint32_t esize;
+};
+struct MapCacheEntry {
+  bool used = false;
+  MapKey key;
+  CUtensorMap map;
+};
+constexpr int kMapCacheEntries = 32;
+// Per thread: no lock, and a map encoded under one thread's current context is only reused there.
+struct MapCache {
+  MapCacheEntry e[kMapCacheEntries];
+  int next = 0;
+};
+thread_local MapCache t_map_cache;
+bool map_cache_get(const MapKey& key, CUtensorMap* out) {
+  MapCache& c = t_map_cache;
+  for (int i = 0; i < kMapCacheEntries; ++i) {
+    if (c.e[i].used && memcmp(&c.e[i].key, &key, sizeof(MapKey)) == 0) {
+      *out = c.e[i].map;
+      return true;
+    }
+  }
+  return false;
+}
+void map_cache_put(const MapKey& key, const CUtensorMap& map) {
+  MapCache& c = t_map_cache;
+  MapCacheEntry& slot = c.e[c.next];
+  c.next = (c.next + 1) % kMapCacheEntries;
+  slot.used = true;
+  slot.key = key;
+  slot.map = map;
 }
 
 struct OperandMap {
@@ -987,6 +995,14 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   const CUtensorMapDataType dt = esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
                                               : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  // A tensor map is a pure function of the arguments below, so the encoded 128 bytes are kept
+  // per thread and reused when the same operand comes back (a layer called every step, the
+  // weights of an MLP): the driver call is then skipped.
+  MapKey key{};
+  key.base = base; key.esize = static_cast<uint32_t>(esize);
+  for (int i = 0; i < 5; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i < 4; ++i) key.strides[i] = strides[i];
+  if (map_cache_get(key, &out->map)) return nullptr;
   EncodeTiledFn enc = encode_fn();
   if (!enc) return "cuTensorMapEncodeTiled is not available from the driver";
   const CUresult r = enc(&out->map, dt, 5, reinterpret_cast<void*>(base), dims, strides, box, estr,
@@ -996,6 +1012,7 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   // Anything else (no current context, driver shut down) is a failure of the call, not a
   // property of the layout: the leading '!' makes the caller report it instead of falling back.
   if (r != CUDA_SUCCESS) return "!cuTensorMapEncodeTiled failed (no usable CUDA context on this thread?)";
+  map_cache_put(key, out->map);
   return nullptr;
 }
 
@@ -1006,18 +1023,32 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   constexpr size_t smem = Cfg::kStages * (Cfg::kStageA + Cfg::kStageB) + 256 /* SmemTail */ +
                           Cfg::kEpiWarps * Cfg::kEpiStage + 1024;
   static_assert(sizeof(SmemTail) <= 256, "barrier block outgrew its slot");
-  static int max_ctas[kMaxDevices] = {0};  // CTAs (1-CTA form) or CTA pairs that can be resident
+  // CTAs (1-CTA form) or CTA pairs that can be resident; concurrent first callers compute the
+  // same value, so relaxed atomics are enough.
+  static std::atomic<int> max_ctas[kMaxDevices];
   auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU, PAIR, MH>;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(threads_for(MH), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = PAIR ? 1 : 0;
-  if (max_ctas[device] == 0) {
+  cudaLaunchAttribute attrs[2];
+  int n_attrs = 0;
+  if (PAIR) {
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 2; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+  }
+  if (dependent_launch_enabled()) {
+    // The kernel's set-up (barriers, TMEM, tensor-map prefetch) may overlap the tail of the
+    // kernel before it in the stream; it waits for that kernel before touching global memory.
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n_attrs;
+  int resident = max_ctas[device].load(std::memory_order_relaxed);
+  if (resident == 0) {
     HODU_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)),
                   HODU_B200_ERR_LAUNCH);
@@ -1028,9 +1059,10 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
       if (cudaOccupancyMaxActiveClusters(&q, kern, &cfg) == cudaSuccess && q >= 1) n = q;
       else cudaGetLastError();
     }
-    max_ctas[device] = n > 0 ? n : 1;
+    resident = n > 0 ? n : 1;
+    max_ctas[device].store(resident, std::memory_order_relaxed);
   }
-  const int units = static_cast<int>(p.num_tiles < static_cast<uint32_t>(max_ctas[device]) ? p.num_tiles : max_ctas[device]);
+  const int units = static_cast<int>(p.num_tiles < static_cast<uint32_t>(resident) ? p.num_tiles : resident);
   cfg.gridDim = dim3(PAIR ? 2 * units : units, 1, 1);
   if (debug_enabled())
     fprintf(stderr, "[hodu_b200] gemm_tc %s: %u tiles of %dx%d, grid %u, %zu B smem, A %s x%u, B %s x%u%s\n",
@@ -1059,12 +1091,6 @@ int launch_shape(int bn, int pair /* 0: 1-CTA, 1: 256x256 pair, 2: 512x256 pair 
 }
 
 }  // namespace
-
-#ifdef HODU_TC_PROFILE
-extern "C" int hodu_b200_debug_read_prof(unsigned long long* out64) {
-  return cudaMemcpyFromSymbol(out64, g_tc_prof, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t limit_ms) {
   wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(st->status, static_cast<uint64_t>(limit_ms) * 1000000ull);
@@ -1245,9 +1271,6 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   const int osz = dtype_size(pb.out_dtype);
   p.out_vec_ok = (reinterpret_cast<uintptr_t>(pb.out) % 16 == 0 && (p.ldc * osz) % 16 == 0 &&
                   (p.out_batch_stride * osz) % 16 == 0) ? 1u : 0u;
-#ifdef HODU_TC_PROFILE
-  if (const char* e = getenv("HODU_TC_EXPERIMENT")) p.out_vec_ok |= static_cast<uint32_t>(atoi(e)) & 14u;
-#endif
   // The tensor core adds into its f32 accumulator with truncation, so the error of a long sum
   // grows with its length (7e-5 of the largest output at K = 8192 with one accumulator per
   // tile, against the 1e-4 bar of the f32 path).  Long f32 products therefore run as
@@ -1259,7 +1282,7 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   // line up with the thirds; the limit below therefore stays at the whole K'.)
   p.k_gen = p.k_blocks;
   p.k_gen_limit = p.k_blocks;
-  if (kind == KIND_TF32 && pb.f32_presplit && (p.out_vec_ok & 1u) && !pb.swiglu && p.k_blocks > 128u)
+  if (kind == KIND_TF32 && pb.f32_presplit && !pb.swiglu && p.k_blocks > 128u)
     p.k_gen = p.k_blocks > 3072u ? 64u : 128u;
 
   int device = 0;

@@ -123,6 +123,13 @@ int host_impl(bool is_dot, int device, int in_dtype, int out_dtype, const void* 
                           static_cast<size_t>(c_elems) * osz};
   r = ensure(hp, need);
   if (r) return r;
+  // Whatever way this call ends, nothing it queued may still be running when the lock is dropped
+  // and the caller gets its host buffers back: an early error return would otherwise leave copies
+  // in flight that read `lhs` / `rhs`, write `out`, or use the staging the next call overwrites.
+  struct DrainOnExit {
+    HostPipe* hp;
+    ~DrainOnExit() { for (int i = 0; i < kSlots; ++i) cudaStreamSynchronize(hp->stream[i]); }
+  } drain{hp};
 
   pb.in_dtype = in_dtype; pb.out_dtype = out_dtype; pb.alpha = sl * sr;
   const bool lanes = host_lanes();
@@ -265,6 +272,80 @@ int host_impl(bool is_dot, int device, int in_dtype, int out_dtype, const void* 
   return 0;
 }
 
+// SwiGLU MLP over host activations: tokens travel in row blocks, the three weight matrices stay
+// where they are (device memory).  Block i: upload x_i -> hidden_i = silu(x_i.Wg) * (x_i.Wu) ->
+// y_i = hidden_i . Wd -> download y_i, on the same three streams as above, so the upload of block
+// i+1 and the download of block i-1 run under the two products of block i.
+int mlp_host_impl(int device, int dtype, const void* x_host, const void* w_gate, const void* w_up,
+                  const void* w_down, void* y_host, const size_t* md, size_t len, uint32_t flags) {
+  if (!md || len != 13) return fail(HODU_B200_ERR_INVALID_INPUT, "swiglu_mlp_host: metadata length %zu, expected 13", len);
+  if (dtype != HODU_DTYPE_BF16 && dtype != HODU_DTYPE_F16)
+    return fail(HODU_B200_ERR_INVALID_KERNEL, "swiglu_mlp_host: unsupported dtype %s", dtype_name(dtype));
+  if (flags != HODU_B200_SWIGLU_ROUND_EACH_OP && flags != HODU_B200_SWIGLU_ROUND_ONCE)
+    return fail(HODU_B200_ERR_INVALID_INPUT, "swiglu_mlp_host: unknown flags %u", flags);
+  for (int i = 0; i < 4; ++i)
+    if (md[i] > (1ull << 32)) return fail(HODU_B200_ERR_INVALID_INPUT, "swiglu_mlp_host: extent out of range");
+  for (int i = 4; i < 13; ++i)
+    if (md[i] > (1ull << 48)) return fail(HODU_B200_ERR_INVALID_INPUT, "swiglu_mlp_host: stride or offset out of range");
+  const int64_t tokens = md[0], d_in = md[1], d_hidden = md[2], d_out = md[3];
+  if (tokens == 0 || d_out == 0) return 0;
+  if (d_in == 0 || d_hidden == 0) return fail(HODU_B200_ERR_INVALID_INPUT, "swiglu_mlp_host: empty feature dimension");
+  if (!x_host || !w_gate || !w_up || !w_down || !y_host) return fail(HODU_B200_ERR_INVALID_INPUT, "null operand pointer");
+  DeviceState* st = device_state(device);
+  if (!st) return HODU_B200_ERR_NOT_INITIALISED;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(HODU_B200_ERR_LAUNCH, "cannot select CUDA device %d", device);
+
+  const int esz = dtype_size(dtype);
+  int64_t per = (tokens + host_slices() - 1) / host_slices();
+  per = (per + 511) / 512 * 512;   // whole 512-row tiles per block
+  const int n_blocks = static_cast<int>((tokens + per - 1) / per);
+  if (n_blocks > kMaxSlices) return fail(HODU_B200_ERR_INVALID_INPUT, "swiglu_mlp_host: too many blocks");
+  HostPipe* hp = &g_pipe[device];
+  std::lock_guard<std::mutex> lock(hp->mu);
+  // staging: all of x, ONE hidden block (the products run in order on one stream), all of y
+  const size_t need[3] = {static_cast<size_t>(tokens) * d_in * esz, static_cast<size_t>(per) * d_hidden * esz,
+                          static_cast<size_t>(tokens) * d_out * esz};
+  int r = ensure(hp, need);
+  if (r) return r;
+  struct DrainOnExit {
+    HostPipe* hp;
+    ~DrainOnExit() { for (int i = 0; i < kSlots; ++i) cudaStreamSynchronize(hp->stream[i]); }
+  } drain{hp};
+  const uint8_t* hx = static_cast<const uint8_t*>(x_host);
+  uint8_t* hy = static_cast<uint8_t*>(y_host);
+  uint8_t* dx = static_cast<uint8_t*>(hp->buf[0]);
+  uint8_t* dh = static_cast<uint8_t*>(hp->buf[1]);
+  uint8_t* dy = static_cast<uint8_t*>(hp->buf[2]);
+  cudaStream_t up = hp->stream[0], comp = hp->stream[1], down = hp->stream[2];
+  for (int i = 0; i < n_blocks; ++i) {
+    const int64_t r0 = i * per, nr = r0 + per <= tokens ? per : tokens - r0;
+    const size_t xo = static_cast<size_t>(r0) * d_in * esz, yo = static_cast<size_t>(r0) * d_out * esz;
+    HODU_CUDA_TRY(cudaMemcpyAsync(dx + xo, hx + xo, static_cast<size_t>(nr) * d_in * esz, cudaMemcpyHostToDevice, up), HODU_B200_ERR_MEMORY);
+    if ((r = hand_over(hp->uploaded[i], up, comp))) return r;
+    Problem g;
+    g.in_dtype = dtype; g.out_dtype = dtype;
+    g.M = nr; g.K = d_in; g.N = d_hidden;
+    g.a.ptr = dx + xo; g.a.stride_r = d_in; g.a.stride_c = 1;
+    g.b.ptr = w_gate; g.b.stride_r = md[4]; g.b.stride_c = md[5]; g.b.offset = md[10];
+    g.b2.ptr = w_up; g.b2.stride_r = md[6]; g.b2.stride_c = md[7]; g.b2.offset = md[11];
+    g.swiglu = true; g.swiglu_flags = flags;
+    g.out = dh;
+    if ((r = run_problem(g, st, comp))) return r;
+    Problem d;
+    d.in_dtype = dtype; d.out_dtype = dtype;
+    d.M = nr; d.K = d_hidden; d.N = d_out;
+    d.a.ptr = dh; d.a.stride_r = d_hidden; d.a.stride_c = 1;
+    d.b.ptr = w_down; d.b.stride_r = md[8]; d.b.stride_c = md[9]; d.b.offset = md[12];
+    d.out = dy + yo;
+    if ((r = run_problem(d, st, comp))) return r;
+    if ((r = hand_over(hp->computed[i], comp, down))) return r;
+    HODU_CUDA_TRY(cudaMemcpyAsync(hy + yo, dy + yo, static_cast<size_t>(nr) * d_out * esz, cudaMemcpyDeviceToHost, down), HODU_B200_ERR_MEMORY);
+  }
+  for (int i = 0; i < kSlots; ++i) HODU_CUDA_TRY(cudaStreamSynchronize(hp->stream[i]), HODU_B200_ERR_LAUNCH);
+  return 0;
+}
+
 }  // namespace
 
 void release_host_pipeline(int device) {
@@ -295,5 +376,9 @@ int hodu_b200_matmul_host(int device, uint8_t in_dtype, uint8_t out_dtype, const
 int hodu_b200_dot_host(int device, uint8_t in_dtype, uint8_t out_dtype, const void* lhs, const void* rhs,
                        void* out, const size_t* md, size_t len, float sl, float sr) {
   return host_impl(true, device, in_dtype, out_dtype, lhs, rhs, out, md, len, sl, sr);
+}
+int hodu_b200_swiglu_mlp_host(int device, uint8_t dtype, const void* x_host, const void* w_gate, const void* w_up,
+                              const void* w_down, void* y_host, const size_t* md, size_t len, uint32_t flags) {
+  return mlp_host_impl(device, dtype, x_host, w_gate, w_up, w_down, y_host, md, len, flags);
 }
 }

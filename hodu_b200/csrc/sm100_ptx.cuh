@@ -18,6 +18,19 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialisation attribute may start while the
+// kernel before it in the stream is still running.  `grid_dependency_wait` returns once that
+// earlier kernel has finished and its writes are visible (at once when there is none, or when
+// the launch did not carry the attribute); `grid_launch_dependents` lets the NEXT kernel in the
+// stream start its own set-up early.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

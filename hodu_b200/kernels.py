@@ -142,6 +142,14 @@ def call_ops_matmul_host(in_dtype: DType, out_dtype: DType, device: int, lhs_hos
              scale_lhs, scale_rhs))
 
 
+def call_ops_swiglu_mlp_host(dtype: DType, device: int, x_host: int, w_gate: int, w_up: int, w_down: int,
+                             y_host: int, metadata: Sequence[int], flags: int = _lib.SWIGLU_ROUND_EACH_OP) -> None:
+    """Host activations in, host result out, device-resident weights (`hodu_b200_swiglu_mlp_host`)."""
+    md = metadata_array(metadata)
+    check(_lib.lib().hodu_b200_swiglu_mlp_host(device, int(dtype), x_host, w_gate, w_up, w_down, y_host, md,
+                                               len(metadata), flags))
+
+
 def last_status(device: int) -> int:
     """Synchronises `device`, returns (and clears) its status word; raises if non-zero."""
     w = C.c_uint32(0)

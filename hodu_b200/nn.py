@@ -71,7 +71,20 @@ class SwiGluMlp:
     def forward(self, x: Tensor) -> Tensor:
         return self.down.forward(self.hidden(x))
 
-    def forward_unfused(self, x: Tensor) -> Tensor:
-        """Only the two projections of the reference composition that are GEMMs run through
-        this library; silu and mul are not this library's kernels, so this form is not offered."""
-        raise HoduError("unfused SwiGLU needs the reference's unary/binary kernels, which are outside this path")
+    def forward_host(self, x_host_ptr: int, y_host_ptr: int, tokens: int) -> None:
+        """The same forward for activations that live in HOST memory (pinned for full copy speed):
+        `x_host_ptr` -> [tokens, in_features] in, `y_host_ptr` -> [tokens, out_features] out, both
+        contiguous and of the weights' dtype.  Row blocks of tokens are uploaded, multiplied and
+        downloaded as one pipelined call; the weights stay on the device.  Returns when the result
+        is complete in host memory."""
+        g, u, d = self.gate.weight, self.up.weight, self.down.weight
+        if any(l.bias is not None for l in (self.gate, self.up, self.down)):
+            raise HoduError("forward_host takes bias-free layers")
+        gt, ut, dt = (w.transpose(-2, -1) for w in (g, u, d))
+        if not (gt.shape == ut.shape and gt.shape[1] == dt.shape[0]):
+            raise HoduError(f"incompatible layer shapes {g.shape}, {u.shape}, {d.shape}")
+        md = [tokens, gt.shape[0], gt.shape[1], dt.shape[1],
+              gt.layout.strides[0], gt.layout.strides[1], ut.layout.strides[0], ut.layout.strides[1],
+              dt.layout.strides[0], dt.layout.strides[1], gt.layout.offset, ut.layout.offset, dt.layout.offset]
+        kernels.call_ops_swiglu_mlp_host(g.dtype, g.device_id, x_host_ptr, g.storage.data_ptr(), u.storage.data_ptr(),
+                                         d.storage.data_ptr(), y_host_ptr, md, self.rounding)

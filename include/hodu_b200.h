@@ -269,6 +269,24 @@ int hodu_b200_dot_host(int device, uint8_t in_dtype, uint8_t out_dtype,
                        float scale_lhs, float scale_rhs);
 
 /*
+ * SwiGLU MLP forward over HOST activations with DEVICE-resident weights:
+ *   y_host[tokens, d_out] = (silu(x . W_gate) * (x . W_up)) . W_down
+ * i.e. "tensor from host data -> three `Linear::forward` calls, silu, mul
+ * (crates/hodu_nn/src/modules/linear.rs:38-47) -> to_cpu_storage" as one pipelined call: tokens
+ * travel in row blocks whose upload, two products and download overlap; the hidden activations
+ * never leave the device.  x_host and y_host are contiguous host arrays (pinned memory gives full
+ * copy speed); w_gate, w_up, w_down are device pointers to the layers' weights.
+ * metadata (13 words) = [tokens, d_in, d_hidden, d_out,
+ *                        wg_stride_k, wg_stride_n, wu_stride_k, wu_stride_n, wd_stride_k, wd_stride_n,
+ *                        wg_off, wu_off, wd_off]   (strides and offsets in elements; a `Linear`
+ * weight stored [out, in] is passed as its transposed view: stride_k = 1, stride_n = in).
+ * dtype: bf16 | f16.  flags as hodu_b200_swiglu.  Returns after y_host is complete.
+ */
+int hodu_b200_swiglu_mlp_host(int device, uint8_t dtype, const void* x_host, const void* w_gate,
+                              const void* w_up, const void* w_down, void* y_host,
+                              const size_t* metadata, size_t metadata_len, uint32_t flags);
+
+/*
  * 2-D f32 product that allocates NOTHING.  It has no counterpart in the reference (whose
  * wrappers allocate on every call: the metadata copy in
  * crates/hodu_cuda_kernels/src/kernels/ops_matrix.rs:572-582).
@@ -297,11 +315,19 @@ int hodu_b200_dot_host(int device, uint8_t in_dtype, uint8_t out_dtype,
  *    Two calls whose kernels can overlap on the GPU (different streams without an ordering
  *    between them) race on it; order them.
  *  - A bounded wait that runs out is recorded in a device word private to this entry point,
- *    not in the word hodu_b200_last_status reads.
+ *    not in the word hodu_b200_last_status reads; hodu_b200_dot_f32_static_status reads it.
  */
 #define HODU_B200_STATIC_SCRATCH_BYTES (32u << 20)
 int hodu_b200_dot_f32_static(int device, void* stream, const void* lhs, const void* rhs, void* out,
                              const size_t* metadata, size_t metadata_len);
+/*
+ * Synchronises `device`, then reads (and clears) the status word of hodu_b200_dot_f32_static.
+ * Zero: every kernel that entry point launched finished its waits.  Non-zero: a bounded wait
+ * gave up and the output of that call is incomplete; the function then returns
+ * HODU_B200_ERR_DEVICE_STATUS.  Like the entry point it belongs to, it allocates nothing and
+ * needs no hodu_b200_init.  No counterpart in the reference.
+ */
+int hodu_b200_dot_f32_static_status(int device, uint32_t* device_status_word);
 
 /* Text for an error code (static storage).  Mirrors `Display for CudaKernelError`
  * (crates/hodu_cuda_kernels/src/error.rs:20-32). */

@@ -28,7 +28,15 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD = os.path.join(HERE, "_build")
 REF = os.path.join(HERE, "_ref")
-DEFAULT_REF_ROOT = os.environ.get("HODU_REFERENCE_ROOT", "/root/reference")
+
+
+def default_ref_root() -> str:
+    """Where the reference checkout is looked for: $HODU_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository.  Neither present: the prebuilt files are used as they are."""
+    env = os.environ.get("HODU_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 
 
 def _run(cmd):
@@ -68,7 +76,8 @@ def _exports(path: str, symbol: str) -> bool:
         return False
 
 
-def build_ref(ref_root: str = DEFAULT_REF_ROOT):
+def build_ref(ref_root: str = ""):
+    ref_root = ref_root or default_ref_root()
     kdir = os.path.join(ref_root, "crates", "hodu_cpu_kernels", "kernels")
     if not os.path.isdir(kdir):
         return None
@@ -99,7 +108,7 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-root", default=DEFAULT_REF_ROOT)
+    ap.add_argument("--ref-root", default="")
     a = ap.parse_args()
     print(build_oracle())
     print(build_ref(a.ref_root) or "reference tree not present: oracle/_ref left as it is")

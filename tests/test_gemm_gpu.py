@@ -343,6 +343,34 @@ def test_f32_long_k_stays_inside_the_bar(m, k, n):
     assert O.rel_err(got, want) <= 2e-5
 
 
+@pytest.mark.parametrize("m,k,n,out_shift", [(256, 40000, 250, 0), (300, 40000, 253, 0), (256, 40000, 256, 1),
+                                             (512, 16384, 130, 3)])
+def test_f32_long_k_with_outputs_that_rule_out_vector_stores(m, k, n, out_shift):
+    """The same bar when the output rows cannot take 16-byte stores (N not a multiple of 4, or an
+    output pointer at an odd element): the accumulator generations still run, through the
+    element-wise store path."""
+    import torch
+    from gpu_util import DEV, to_dev
+    rng = np.random.default_rng(k + n)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    md = dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n)))
+    ta, tb = to_dev(a), to_dev(b)
+    buf = torch.full((m * n + out_shift + 64,), 7.0, dtype=torch.float32, device=DEV)
+    out = buf[out_shift:]
+    prev = K.force_path(TENSOR)
+    try:
+        K.call_ops_dot(K.dot.F32, 0, ta.data_ptr(), tb.data_ptr(), out.data_ptr(), md, 0)
+        assert K.last_path() == TENSOR
+    finally:
+        K.force_path(prev)
+    assert K.last_status(0) == 0
+    host = buf.cpu().numpy()
+    assert (host[:out_shift] == 7.0).all() and (host[out_shift + m * n:] == 7.0).all()
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32).reshape(-1)
+    assert O.rel_err(host[out_shift:out_shift + m * n], want) <= 2e-5
+
+
 def test_output_beyond_two_to_the_31_elements():
     """Maximum sizes: an output of 66000 x 33000 = 2.18e9 elements (4.4 GB of bf16), so element
     and byte offsets pass 2^31 and 2^32; rows sampled from both ends and the middle are checked
