@@ -108,6 +108,7 @@ class ClockSampler:
     def __init__(self, uuid: str):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
+        self._first = threading.Event()
         self._t = None
         try:
             import pynvml
@@ -134,18 +135,26 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            time.sleep(0.0002)
+            self._first.set()
+            time.sleep(0.0001)
 
     def __enter__(self):
         if self.nv is not None:
+            # a short switch interval, so that the sampling thread is not kept waiting for the
+            # interpreter lock while the main thread issues launches
+            self._switch = sys.getswitchinterval()
+            sys.setswitchinterval(1e-4)
             self._t = threading.Thread(target=self._run, daemon=True)
             self._t.start()
+            self._first.wait(0.5)   # the region starts with the sampler already running
+            self.samples.clear()
         return self
 
     def __exit__(self, *a):
         self._stop.set()
         if self._t is not None:
             self._t.join()
+            sys.setswitchinterval(self._switch)
 
     def summary(self):
         if not self.samples:

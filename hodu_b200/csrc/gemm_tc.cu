@@ -98,6 +98,7 @@ struct TcParams {
   OperandLoad a, b;
   uint32_t idesc;
   uint32_t out_vec_ok;    // rows of `out` allow 16-byte stores
+  uint32_t out_tma;       // map_out describes `out`: a CTA's last tile leaves through TMA stores
   uint32_t swiglu_flags;
   uint32_t bias_flags;
   float alpha;
@@ -303,6 +304,20 @@ __device__ __forceinline__ void pack_chunk(const uint32_t (&v)[32], uint32_t (&p
     }
   }
 }
+// Lane l writes the 64 bytes `w` of row l of a 32-row x 64-byte block at `stage` (512-byte
+// aligned): 16-byte pieces XOR-swizzled by (row / 2) % 4, which is both bank-conflict-free and
+// exactly the layout a tensor map with 64-byte swizzle reads.
+__device__ __forceinline__ void stage_write_row64(uint32_t stage, uint32_t lane, const uint32_t* w) {
+  const uint32_t wsw = (lane >> 1) & 3u;
+#pragma unroll
+  for (uint32_t j = 0; j < 4; ++j) {
+    const uint32_t addr = stage + lane * 64u + ((j ^ wsw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]), "r"(w[4 * j + 1]),
+                 "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                 : "memory");
+  }
+}
+
 template <int KWORDS>
 __device__ __forceinline__ void store_packed_staged(uint8_t* out_tile, unsigned long long pitch_bytes,
                                                     uint32_t row0, uint32_t rows_total, uint32_t col_byte0,
@@ -353,7 +368,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
                                               const CUtensorMap* map0, const CUtensorMap* map1,
                                               SmemTail* tail, uint32_t smem_operand, uint32_t rank,
                                               uint32_t first_tile, uint32_t tile_step,
-                                              uint32_t code) {
+                                              const TileCoord& first_tc, uint32_t code) {
   using Cfg = TileCfg<BN, PAIR, MH>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kStageBytes = IS_A ? Cfg::kStageA : Cfg::kStageB;
@@ -364,7 +379,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
   uint32_t s = 0, ph = 0, issued = 0;
   bool ok = true;
   for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-    const TileCoord tc = decode_tile(p, t);
+    const TileCoord tc = t == first_tile ? first_tc : decode_tile(p, t);
     const uint32_t b2 = tc.batch % p.bdim2;
     const uint32_t tmp = tc.batch / p.bdim2;
     const uint32_t b1 = tmp % p.bdim1;
@@ -421,7 +436,8 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
 template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
 __global__ void __launch_bounds__(threads_for(MH), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_b2, const TcParams p) {
+               const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_out,
+               const TcParams p) {
   static_assert(MH == 1 || (PAIR && BN == 256), "two M-halves per CTA exist for the pair form only");
   using Cfg = TileCfg<BN, PAIR, MH>;
   constexpr int kStages = Cfg::kStages;
@@ -439,7 +455,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base_u32 - raw_u32);
-  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + kStages * (kStageA + kStageB));
+  // [operand ring][epilogue staging: 2 KB per epilogue warp, 1 KB aligned][barriers and flags]
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + kStages * (kStageA + kStageB) + Cfg::kEpiWarps * Cfg::kEpiStage);
   const uint32_t smem_a = base_u32;
   const uint32_t smem_b = base_u32 + kStages * kStageA;
 
@@ -451,6 +468,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile uint32_t* abort_flag = &tail->abort_flag;
 
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_a);   // first: the descriptor fetch runs under the rest of the set-up
+    prefetch_tensormap(&map_b);
+    if constexpr (SWIGLU) prefetch_tensormap(&map_b2);
+    prefetch_tensormap(&map_out);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&tail->full[s]), 2);   // one arrive(+tx) per operand producer
       mbar_init(smem_u32(&tail->empty[s]), 1);  // one commit arrive (delivered to both CTAs of a pair)
@@ -462,17 +483,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     mbar_init(smem_u32(&tail->drain), 1);
     tail->abort_flag = 0;
     fence_barrier_init();
-    prefetch_tensormap(&map_a);
-    prefetch_tensormap(&map_b);
-    if constexpr (SWIGLU) prefetch_tensormap(&map_b2);
   }
   if (warp == 1) {
     tmem_alloc<CG>(smem_u32(&tail->tmem_base), Cfg::kTmemCols);
     tmem_relinquish<CG>();
   }
   tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
+  // One barrier for both purposes: the CTA's own barriers and TMEM address are visible to all
+  // its threads, and (pair forms) the peer's barriers exist before anything signals them.  The
+  // first tile's coordinates, which need nothing from anybody, are worked out between the
+  // arrive and the wait.
+  if constexpr (PAIR) cluster_arrive();
+  const TileCoord first_tc = decode_tile(p, first_tile < p.num_tiles ? first_tile : 0u);
+  if constexpr (PAIR) cluster_wait();
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tail->tmem_base);
   const uint32_t code_base = 0x80000000u | ((blockIdx.x & 0xFFFFu) << 4);
@@ -487,14 +511,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------ producer of A
     if (lane == 0)
       producer_role<BN, SWIGLU, PAIR, MH, true>(p, p.a, &map_a, &map_a, tail, smem_a, rank, first_tile,
-                                            tile_step, code_base | 1u);
+                                                tile_step, first_tc, code_base | 1u);
     __syncwarp();
   } else if (warp == 6) {
     // ------------------------------------------------------------ producer of B
     if (lane == 0) {
       const CUtensorMap* m0 = (PAIR && SWIGLU && rank == 1) ? &map_b2 : &map_b;
       producer_role<BN, SWIGLU, PAIR, MH, false>(p, p.b, m0, &map_b2, tail, smem_b, rank, first_tile,
-                                             tile_step, code_base | 5u);
+                                                 tile_step, first_tc, code_base | 5u);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -589,7 +613,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t col_group = e_group % kColGroups;      // which share of the output columns
     constexpr uint32_t kChunks = kOutCols / 32 / kColGroups;
     const uint32_t e_warp = warp < 6u ? warp - 2u : warp - 3u;  // index among the epilogue warps
-    const uint32_t stage_buf = base_u32 + kStages * (kStageA + kStageB) + 256u + e_warp * Cfg::kEpiStage;
+    const uint32_t stage_buf = base_u32 + kStages * (kStageA + kStageB) + e_warp * Cfg::kEpiStage;
     constexpr bool kStaged = (OUT == OUT_F32 || OUT == OUT_I32 || OUT == OUT_BF16 || OUT == OUT_F16);
     const uint32_t osz = OutBytes<OUT>::value;
     const uint32_t tmem_empty0 =
@@ -599,7 +623,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (uint32_t t = first_tile; epi_ok && t < p.num_tiles; t += tile_step) {
     // Where this tile's rows go: worked out BEFORE the wait for the accumulator (these divisions
     // and 64-bit products measured ~800 cycles, which were exposed after the wait).
-    const TileCoord tc = decode_tile(p, t);
+    const TileCoord tc = t == first_tile ? first_tc : decode_tile(p, t);
     const uint32_t row = tc.mt * kTileM + rank * 128u * MH + half * 128u + q * 32u + lane;
     const uint32_t n0 = tc.nt * kOutCols;
     const bool row_ok = row < p.M;
@@ -673,7 +697,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // SwiGLU in the op-by-op rounding form first rounds gate and up to the storage dtype, so
       // the two can leave TMEM as packed 16-bit pairs and silu / product run after the release.
       const bool swiglu_split = SWIGLU && p.swiglu_flags == HODU_B200_SWIGLU_ROUND_EACH_OP;
-      if (kEarlyRelease && staged && (!SWIGLU || swiglu_split)) {
+      // A CTA's LAST tile has no successor waiting for the accumulator, so it takes the chunk by
+      // chunk path below instead: its stores start after the first TMEM load rather than after
+      // the last, which shortens the tail of the launch (all of it, when every CTA has one tile).
+      const bool last_tile = t + tile_step >= p.num_tiles;
+      // ... and when the output has a tensor map, through TMA: by now every MMA of this CTA has
+      // retired, so the operand ring is idle and each epilogue warp takes 8 KB of it as staging.
+      // The warp converts a chunk, writes it there, and one lane hands it to the TMA unit, which
+      // streams the stores at the rate the SM's store port allows while the warp is already
+      // converting the next chunk; tails of M and N are clipped by the tensor map.
+      bool tail_tma = false;
+      if constexpr (kStaged) tail_tma = staged && last_tile && p.out_tma != 0u && !(kGenerations && p.k_gen < p.k_blocks);
+      if (tail_tma) {
+        if constexpr (kStaged) {
+          constexpr uint32_t kWords = ChunkWords<OUT>::value;      // 16 or 32 words per lane and chunk
+          constexpr uint32_t kChunkBytes = kWords * 4u * 32u;      // 2 KB or 4 KB
+          constexpr uint32_t kBufs = 8192u / kChunkBytes;
+          const uint32_t ring = base_u32 + e_warp * 8192u;
+          const uint32_t row0 = row - lane;
+          uint32_t n_issued = 0;
+#pragma unroll 1
+          for (uint32_t c = col_group * kChunks; c < (col_group + 1u) * kChunks; ++c) {
+            const uint32_t col = n0 + c * 32u;
+            if (col >= p.N) break;  // uniform over the warp
+            uint32_t v[32];
+            load_chunk(c, v);
+            uint32_t pk[kWords];
+            pack_chunk<OUT>(v, pk);
+            const uint32_t buf = ring + (n_issued % kBufs) * kChunkBytes;
+            if (n_issued >= kBufs) {   // the store that last read this buffer must be done with it
+              if (lane == 0) bulk_wait_group_read<static_cast<int>(kBufs) - 1>();
+              __syncwarp();
+            }
+#pragma unroll
+            for (uint32_t g = 0; g < kWords / 16u; ++g) stage_write_row64(buf + g * 2048u, lane, &pk[16u * g]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+#pragma unroll
+              for (uint32_t g = 0; g < kWords / 16u; ++g) {
+                const uint32_t cg = col + g * (64u / OutBytes<OUT>::value);
+                if (cg < p.N)
+                  tma_store_3d(&map_out, buf + g * 2048u, static_cast<int32_t>(cg), static_cast<int32_t>(row0),
+                               static_cast<int32_t>(tc.batch));
+              }
+            }
+            if (lane == 0) bulk_commit_group();
+            ++n_issued;
+          }
+          if (lane == 0) bulk_wait_group_read<0>();   // the ring may go away once the stores have read it
+          __syncwarp();
+        }
+      } else if (kEarlyRelease && staged && (!SWIGLU || swiglu_split) && !last_tile) {
         uint32_t pk[kChunks][16];
         [[maybe_unused]] uint32_t pu[SWIGLU ? kChunks : 1][16];
 #pragma unroll
@@ -766,8 +841,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // A CTA of a pair may not leave (or free TMEM) while its peer can still read its shared
   // memory, signal its barriers or write its TMEM.
   tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (PAIR) cluster_sync_all();
+  if constexpr (PAIR) cluster_sync_all();   // also a barrier over this CTA's own threads
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, Cfg::kTmemCols);
@@ -791,7 +866,11 @@ __global__ void wait_timeout_probe_kernel(uint32_t* status, uint64_t limit_ns) {
 }
 
 // -------------------------------------------------------------- host side
-// HODU_B200_DEBUG=1 prints each tensor-core launch configuration to stderr.
+// HODU_B200_DEBUG=1: every tensor-core launch prints its configuration to stderr, has its tile
+// arithmetic, stage sizes, TMEM columns and TMA coordinate ranges checked on the host before it
+// runs, and is followed by a stream synchronisation and a read of the device status word, so a
+// fault or a wait that gave up is reported by the call that caused it.  For debugging only: it
+// serialises the stream and must not be used inside a stream capture.
 bool debug_enabled() {
   static const bool on = [] { const char* e = getenv("HODU_B200_DEBUG"); return e && e[0] == '1'; }();
   return on;
@@ -828,6 +907,7 @@ struct MapKey {
   uint64_t strides[4];
   uint32_t box[5];
   uint32_t esize;
+  uint32_t kind;   // 0: operand map (5-D, 128-byte swizzle), 1: output map (3-D, 64-byte swizzle)
 };
 struct MapCacheEntry {
   bool used = false;
@@ -947,7 +1027,7 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   const int64_t s_k = k_is_col ? op.stride_c : op.stride_r;
   const uintptr_t base = reinterpret_cast<uintptr_t>(op.ptr) + static_cast<uintptr_t>(op.offset) * esize;
   if (base % 16 != 0) return "operand base address is not 16-byte aligned";
-  if (mn > 0xFFFFFFFFll || kk > 0xFFFFFFFFll) return "extent exceeds 2^32";
+  if (mn > 0x7FFFFFFFll || kk > 0x7FFFFFFFll) return "extent exceeds 2^31 (TMA coordinates are signed 32-bit)";
 
   const int cls = classify_operand(op, esize, rows, cols, k_is_col);
   if (cls < 0) return "neither matrix index is contiguous with a 16-byte-multiple pitch";
@@ -1016,12 +1096,39 @@ const char* build_operand_map(const Operand& op, int esize, int64_t rows, int64_
   return nullptr;
 }
 
+// Tensor map of the output for the TMA stores of a CTA's last tile: dims {N, M, batches}, box
+// {64 bytes of a row, 32 rows, 1}, 64-byte swizzle (the layout stage_write_row64 produces).
+// False when the output cannot be described (then the kernel keeps its ordinary stores).
+bool build_output_map(const TcParams& p, int osz, uint32_t batches, CUtensorMap* out) {
+  if (!(p.out_vec_ok & 1u) || (osz != 2 && osz != 4)) return false;
+  const uint64_t row_pitch = p.ldc * static_cast<uint64_t>(osz), batch_pitch = p.out_batch_stride * static_cast<uint64_t>(osz);
+  if (row_pitch >= (1ull << 40) || batch_pitch >= (1ull << 40) || p.N == 0 || p.M == 0 || batches == 0) return false;
+  cuuint64_t dims[3] = {p.N, p.M, batches};
+  cuuint64_t strides[2] = {row_pitch, batches > 1 ? batch_pitch : row_pitch * p.M};
+  if (strides[1] % 16 != 0 || strides[1] >= (1ull << 40)) return false;
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(64 / osz), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  MapKey key{};
+  key.base = reinterpret_cast<uintptr_t>(p.out); key.esize = static_cast<uint32_t>(osz); key.kind = 1;
+  for (int i = 0; i < 3; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i < 2; ++i) key.strides[i] = strides[i];
+  if (map_cache_get(key, out)) return true;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const CUresult r = enc(out, osz == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.out, dims,
+                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  map_cache_put(key, *out);
+  return true;
+}
+
 template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
-int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mo,
                 const TcParams& p, int device, int sm_count, cudaStream_t stream) {
   using Cfg = TileCfg<BN, PAIR, MH>;
-  constexpr size_t smem = Cfg::kStages * (Cfg::kStageA + Cfg::kStageB) + 256 /* SmemTail */ +
-                          Cfg::kEpiWarps * Cfg::kEpiStage + 1024;
+  constexpr size_t smem = Cfg::kStages * (Cfg::kStageA + Cfg::kStageB) + Cfg::kEpiWarps * Cfg::kEpiStage +
+                          256 /* SmemTail */ + 1024 /* alignment slack */;
   static_assert(sizeof(SmemTail) <= 256, "barrier block outgrew its slot");
   // CTAs (1-CTA form) or CTA pairs that can be resident; concurrent first callers compute the
   // same value, so relaxed atomics are enough.
@@ -1069,23 +1176,55 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
             PAIR ? "pair" : "1-CTA", p.num_tiles, PAIR ? 256 * MH : 128, SWIGLU ? BN / 2 : BN, cfg.gridDim.x, smem,
             p.a.mn_major ? "M-major" : "K-major", p.a.boxes, p.b.mn_major ? "N-major" : "K-major", p.b.boxes,
             p.b.slab_dim ? " (slab dim)" : "");
-  HODU_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, mb2, p), HODU_B200_ERR_LAUNCH);
+  if (debug_enabled()) {
+    // Everything the kernel takes on trust, checked on the host before it runs.
+    constexpr uint32_t kTileRows = PAIR ? 256u * MH : 128u, kTileCols = SWIGLU ? BN / 2 : BN;
+    const char* bad = nullptr;
+    if (p.a.boxes * p.a.box_bytes != static_cast<uint32_t>(Cfg::kStageA)) bad = "lhs boxes do not fill a stage";
+    else if (p.b.boxes * p.b.box_bytes != static_cast<uint32_t>(Cfg::kStageB)) bad = "rhs boxes do not fill a stage";
+    else if (Cfg::kTmemCols > 512 || (Cfg::kTmemCols & (Cfg::kTmemCols - 1)) != 0) bad = "TMEM columns not a power of two <= 512";
+    else if (static_cast<uint64_t>(p.tiles_m) * kTileRows < p.M || static_cast<uint64_t>(p.tiles_m - 1) * kTileRows >= p.M)
+      bad = "row tiles do not cover M exactly";
+    else if (static_cast<uint64_t>(p.tiles_n) * kTileCols < p.N || static_cast<uint64_t>(p.tiles_n - 1) * kTileCols >= p.N)
+      bad = "column tiles do not cover N exactly";
+    else if (static_cast<uint64_t>(p.k_blocks) * p.bk < p.K || static_cast<uint64_t>(p.k_blocks - 1) * p.bk >= p.K)
+      bad = "k-blocks do not cover K exactly";
+    else if (static_cast<uint64_t>(p.tiles_m) * kTileRows > 0x7FFFFFFFull || static_cast<uint64_t>(p.tiles_n) * BN > 0x7FFFFFFFull ||
+             static_cast<uint64_t>(p.k_blocks) * p.bk > 0x7FFFFFFFull)
+      bad = "a TMA coordinate would not fit 32 signed bits";
+    else if (p.num_tiles % (p.tiles_m * p.tiles_n) != 0) bad = "tile count is not batches x tiles_m x tiles_n";
+    else if (p.ldc < p.N || p.out_batch_stride < static_cast<unsigned long long>(p.M - 1) * p.ldc + p.N) bad = "output rows or batches overlap";
+    else if (p.k_gen == 0 || p.k_gen > p.k_blocks || p.k_gen_limit > p.k_blocks) bad = "accumulator generations out of range";
+    else if (cfg.gridDim.x == 0 || (PAIR && (cfg.gridDim.x & 1u))) bad = "grid size";
+    else if (smem > 232448) bad = "shared memory beyond the 227 KB a CTA can have";
+    if (bad) return fail(HODU_B200_ERR_LAUNCH, "debug check before launch: %s", bad);
+  }
+  HODU_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, mb2, mo, p), HODU_B200_ERR_LAUNCH);
   count_launch();
+  if (debug_enabled()) {
+    // ... and the outcome, at once: wait for the kernel, then read what its bounded waits recorded.
+    HODU_CUDA_TRY(cudaStreamSynchronize(stream), HODU_B200_ERR_LAUNCH);
+    uint32_t w = 0;
+    HODU_CUDA_TRY(cudaMemcpy(&w, p.status, sizeof(w), cudaMemcpyDeviceToHost), HODU_B200_ERR_MEMORY);
+    if (w != 0)
+      return fail(HODU_B200_ERR_DEVICE_STATUS, "debug check after launch: device status word 0x%08x (cta %u, wait %u)", w,
+                  (w >> 4) & 0xFFFFu, w & 0xFu);
+  }
   return 0;
 }
 
 template <int KIND, int OUT, bool SWIGLU>
 int launch_shape(int bn, int pair /* 0: 1-CTA, 1: 256x256 pair, 2: 512x256 pair */, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
-                 const TcParams& p, int device, int sm_count, cudaStream_t stream) {
-  if (pair == 2) return launch_inst<KIND, 256, OUT, SWIGLU, true, 2>(ma, mb, mb2, p, device, sm_count, stream);
-  if (pair == 1) return launch_inst<KIND, 256, OUT, SWIGLU, true, 1>(ma, mb, mb2, p, device, sm_count, stream);
+                 const CUtensorMap& mo, const TcParams& p, int device, int sm_count, cudaStream_t stream) {
+  if (pair == 2) return launch_inst<KIND, 256, OUT, SWIGLU, true, 2>(ma, mb, mb2, mo, p, device, sm_count, stream);
+  if (pair == 1) return launch_inst<KIND, 256, OUT, SWIGLU, true, 1>(ma, mb, mb2, mo, p, device, sm_count, stream);
   if constexpr (SWIGLU) {
-    return launch_inst<KIND, 256, OUT, true, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
+    return launch_inst<KIND, 256, OUT, true, false, 1>(ma, mb, mb2, mo, p, device, sm_count, stream);
   } else {
     switch (bn) {
-      case 256: return launch_inst<KIND, 256, OUT, false, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
-      case 128: return launch_inst<KIND, 128, OUT, false, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
-      default: return launch_inst<KIND, 64, OUT, false, false, 1>(ma, mb, mb2, p, device, sm_count, stream);
+      case 256: return launch_inst<KIND, 256, OUT, false, false, 1>(ma, mb, mb2, mo, p, device, sm_count, stream);
+      case 128: return launch_inst<KIND, 128, OUT, false, false, 1>(ma, mb, mb2, mo, p, device, sm_count, stream);
+      default: return launch_inst<KIND, 64, OUT, false, false, 1>(ma, mb, mb2, mo, p, device, sm_count, stream);
     }
   }
 }
@@ -1103,7 +1242,7 @@ int launch_wait_timeout_probe(DeviceState* st, cudaStream_t stream, uint32_t lim
 bool tc_operand_describable(const Problem& pb, const Operand& op, bool is_lhs, int esize) {
   const int64_t rows = is_lhs ? pb.M : pb.K, cols = is_lhs ? pb.K : pb.N;
   const uintptr_t base = reinterpret_cast<uintptr_t>(op.ptr) + static_cast<uintptr_t>(op.offset) * esize;
-  if (base % 16 != 0 || rows > 0xFFFFFFFFll || cols > 0xFFFFFFFFll) return false;
+  if (base % 16 != 0 || rows > 0x7FFFFFFFll || cols > 0x7FFFFFFFll) return false;
   if (classify_operand(op, esize, rows, cols, is_lhs) < 0) return false;
   for (int d = 0; d < pb.batch_ndim; ++d)
     if (pb.batch_shape[d] > 1 && op.bstride[d] != 0 && !pitch_ok(op.bstride[d], esize)) return false;
@@ -1288,8 +1427,15 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   int device = 0;
   cudaGetDevice(&device);
 
+  // The output's own tensor map, when it has one (HODU_B200_TMA_STORE=0 keeps ordinary stores).
+  CUtensorMap out_map;
+  memset(&out_map, 0, sizeof(out_map));
+  static const bool tma_store_on = [] { const char* e = getenv("HODU_B200_TMA_STORE"); return !(e && e[0] == '0'); }();
+  p.out_tma = (tma_store_on && build_output_map(p, osz, static_cast<uint32_t>(pb.batches), &out_map)) ? 1u : 0u;
+  if (p.out_tma == 0u) out_map = oa.map;   // a valid descriptor for the prefetch; never used for a store
+
 #define HODU_TC(KIND, OUTE, SW) \
-  return launch_shape<KIND, OUTE, SW>(bn, form, oa.map, ob.map, ob2.map, p, device, st->sm_count, stream)
+  return launch_shape<KIND, OUTE, SW>(bn, form, oa.map, ob.map, ob2.map, out_map, p, device, st->sm_count, stream)
   if (pb.swiglu) {
     if (kind != KIND_F16) { *why = "SwiGLU epilogue exists for bf16/f16 only"; return 1; }
     if (pb.out_dtype == HODU_DTYPE_BF16) HODU_TC(KIND_F16, OUT_BF16, true);

@@ -126,6 +126,21 @@ __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// Tiled 3-D store of this CTA's shared memory to global memory (bulk async group completion).
+// c0 is the innermost coordinate; c0 * element size must be a multiple of 16 bytes and no
+// coordinate may be negative.  Elements of the box that fall outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // shared::cta address -> shared::cluster address of the same offset in CTA `cta_rank`.
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
   uint32_t r;
@@ -303,6 +318,15 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
+}
+// The two halves of a cluster-wide barrier: every thread of every CTA arrives, and may do work
+// that needs nothing from its peers before it waits.  A completed cluster barrier also orders the
+// threads of ONE CTA among themselves, so it stands in for __syncthreads() where both are due.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
