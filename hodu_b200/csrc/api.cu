@@ -30,6 +30,7 @@ std::atomic<bool> g_state_ready[kMaxDevices];
 constexpr long long kTensorMinWork = 1ll << 21;     // M*N*K*batches
 constexpr long long kTensorMinWorkRelayout = 1ll << 24;  // an operand copy precedes the product
 constexpr long long kTensorMinWorkF32 = 1ll << 24;  // f32 pays two operand-split launches first
+constexpr long long kTensorMinWorkF32Fused = 1ll << 18;  // ... unless the one-kernel form takes the product
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -310,6 +311,13 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream) {
       if (r2 < 0) return r2;
     }
     if (forced_tc) return fail(HODU_B200_ERR_INVALID_INPUT, "tensor-core path refused: %s", why);
+  }
+  if (!want_tc && forced == HODU_B200_PATH_AUTO && pb.in_dtype == HODU_DTYPE_F32 && work >= kTensorMinWorkF32Fused) {
+    // too small for the split-operand path, but the one-kernel f32 form costs a single launch
+    const char* why = "";
+    const int r = launch_gemm_f32_fused(pb, st, stream, &why);
+    if (r == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
+    if (r < 0) return r;
   }
   set_last_path(HODU_B200_PATH_SIMT);
   return launch_gemm_simt(pb, st, stream);

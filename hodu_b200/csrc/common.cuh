@@ -63,6 +63,16 @@ struct DeviceGuard {
   ~DeviceGuard();
 };
 
+// cuTensorMapEncodeTiled, fetched from the driver once (null if the driver has none).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn tensor_map_encoder();
+// HODU_B200_DEBUG=1 (see gemm_tc.cu).
+bool debug_enabled();
+// Whether kernels are launched with programmatic stream serialisation (HODU_B200_PDL=0: no).
+bool dependent_launch_enabled();
+
 void count_launch(unsigned n = 1);
 void set_last_path(int path);
 int forced_path();
@@ -116,6 +126,11 @@ int launch_gemm_tc_relayout(const Problem& pb, DeviceState* st, cudaStream_t str
 // stream-ordered allocator; `launch_gemm_f32_split` uses the scratch it is given.
 size_t gemm_f32_scratch_bytes(const Problem& pb);
 int launch_gemm_f32(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// One-kernel form for small f32 products (gemm_f32_fused.cu): raw f32 tiles arrive by TMA, are
+// split into TF32 high and low parts in shared memory, multiplied on the tensor cores, and the K
+// slices of a tile are added across a thread-block cluster.  No scratch memory, one launch.
+// Return convention as launch_gemm_tc (1 = not applicable, nothing launched).
+int launch_gemm_f32_fused(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
 int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t stream, void* scratch,
                           size_t scratch_bytes, const char** why);
 // One tiny kernel whose only wait can never be satisfied; it gives up after limit_ms.

@@ -187,6 +187,13 @@ int launch_gemm_f32_split(const Problem& pb, DeviceState* st, cudaStream_t strea
 
 // Allocates the scratch on `stream` (stream-ordered pool), runs the split product, frees it.
 int launch_gemm_f32(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
+  // Small products first try the one-kernel form (no scratch, one launch); a forced tile form
+  // keeps the split-operand path, which is the one that has tile forms.
+  const int forced = forced_path();
+  if (forced == HODU_B200_PATH_AUTO || forced == HODU_B200_PATH_TENSOR) {
+    const int rf = launch_gemm_f32_fused(pb, st, stream, why);
+    if (rf != 1) return rf;
+  }
   const size_t bytes = gemm_f32_scratch_bytes(pb);
   if (bytes == 0) { *why = "more than three batch dims"; return 1; }
   void* scratch = nullptr;

@@ -34,11 +34,41 @@
 #include <atomic>
 #include <mutex>
 
+#include "bounded_wait.cuh"
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
 namespace hodu_b200 {
 using namespace ptx;
+
+// HODU_B200_PDL=0 launches the tensor-core kernels without programmatic dependent launch.
+bool dependent_launch_enabled() {
+  static const bool on = [] { const char* e = getenv("HODU_B200_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+// HODU_B200_DEBUG=1: every tensor-core launch prints its configuration to stderr, has its tile
+// arithmetic, stage sizes, TMEM columns and TMA coordinate ranges checked on the host before it
+// runs, and is followed by a stream synchronisation and a read of the device status word, so a
+// fault or a wait that gave up is reported by the call that caused it.  For debugging only: it
+// serialises the stream and must not be used inside a stream capture.
+bool debug_enabled() {
+  static const bool on = [] { const char* e = getenv("HODU_B200_DEBUG"); return e && e[0] == '1'; }();
+  return on;
+}
+
+EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
 
 namespace {
 
@@ -49,7 +79,6 @@ constexpr int kHalfA = BM * 128;        // bytes: 128 rows (or M elements) x 128
 // two such groups per accumulator, each draining half of the columns (16 epilogue warps).
 constexpr int epi_col_groups(int mh) { return mh == 2 ? 2 : 1; }
 constexpr int threads_for(int mh) { return 96 + 128 * mh * epi_col_groups(mh); }
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, OUT_I8 = 5 };
 
@@ -108,36 +137,6 @@ struct TcParams {
   void* out;
   uint32_t* status;
 };
-
-// -------------------------------------------------------------- bounded waits
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
-                                             volatile uint32_t* abort_flag, uint32_t* status,
-                                             uint32_t code, uint64_t limit_ns = kWaitLimitNs) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 0xFFu) == 0) {
-      if (*abort_flag) return false;
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > limit_ns) {
-        *abort_flag = 1;
-        atomicCAS(status, 0u, code);
-        return false;
-      }
-    }
-  }
-}
-// Used only after an abort: give work already in flight a short time to land.
-__device__ __forceinline__ void wait_drain(uint32_t bar, uint32_t parity) {
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (mbar_try_wait(bar, parity)) return;
-    if ((i & 0xFFu) == 0xFFu && globaltimer_ns() - t0 > 200000000ull) return;
-  }
-}
 
 struct TileCoord {
   uint32_t batch, mt, nt;
@@ -866,39 +865,7 @@ __global__ void wait_timeout_probe_kernel(uint32_t* status, uint64_t limit_ns) {
 }
 
 // -------------------------------------------------------------- host side
-// HODU_B200_DEBUG=1: every tensor-core launch prints its configuration to stderr, has its tile
-// arithmetic, stage sizes, TMEM columns and TMA coordinate ranges checked on the host before it
-// runs, and is followed by a stream synchronisation and a read of the device status word, so a
-// fault or a wait that gave up is reported by the call that caused it.  For debugging only: it
-// serialises the stream and must not be used inside a stream capture.
-bool debug_enabled() {
-  static const bool on = [] { const char* e = getenv("HODU_B200_DEBUG"); return e && e[0] == '1'; }();
-  return on;
-}
-
-// HODU_B200_PDL=0 launches the tensor-core kernels without programmatic dependent launch.
-bool dependent_launch_enabled() {
-  static const bool on = [] { const char* e = getenv("HODU_B200_PDL"); return !(e && e[0] == '0'); }();
-  return on;
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
+EncodeTiledFn encode_fn() { return tensor_map_encoder(); }
 
 // Everything cuTensorMapEncodeTiled is given (swizzle, interleave, promotion and fill are fixed).
 struct MapKey {

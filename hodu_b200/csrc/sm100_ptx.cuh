@@ -113,6 +113,14 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// Tiled 2-D load global -> this CTA's shared memory, completion on an mbarrier of this CTA.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
 // The same load issued by one CTA of a 2-CTA pair: data lands in the issuing CTA's
 // shared memory, completion may be signalled on an mbarrier of either CTA of the pair
 // (`bar` is a shared::cluster address, see mapa_shared).

@@ -43,6 +43,7 @@ def test_debug_mode_checks_every_launch_and_results_stay_right():
     r = subprocess.run([sys.executable, "-c", CODE % (ROOT, os.path.join(ROOT, "tests"))], capture_output=True,
                        text=True, timeout=900, env=env)
     assert r.returncode == 0 and "checked 13" in r.stdout, r.stdout[-800:] + r.stderr[-2000:]
-    lines = [l for l in r.stderr.splitlines() if l.startswith("[hodu_b200] gemm_tc")]
+    lines = [l for l in r.stderr.splitlines() if l.startswith("[hodu_b200] gemm_")]
     assert len(lines) >= 13, r.stderr[-1500:]       # one line per tensor-core launch
     assert any("pair" in l for l in lines) and any("1-CTA" in l for l in lines)
+    assert any("gemm_f32_fused" in l for l in lines)   # the f32 product took the one-kernel form

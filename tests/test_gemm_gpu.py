@@ -260,13 +260,17 @@ def test_auto_path_selection_and_refusal():
         gpu_matmul(ai, ai, dot_metadata(Layout.from_shape((64, 64)), Layout.from_shape((64, 64))), O.I32,
                    is_dot=True, path=TENSOR)
     assert e.value.kind == "invalid input" and "tensor-core path refused" in str(e.value)
-    # f32: small products stay on the CUDA cores, large ones take the split-TF32 tensor path
-    a, la = operand(rng, O.F32, 128, 128, "c")
+    # f32: tiny products stay on the CUDA cores, the rest runs as split TF32 on the tensor cores
+    # (one kernel for small products, the operand-split path for large ones)
+    a, la = operand(rng, O.F32, 32, 32, "c")
     _, path = gpu_matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)
     assert path == SIMT
-    a, la = operand(rng, O.F32, 512, 512, "c")
-    _, path = gpu_matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)
-    assert path == TENSOR
+    for d, launches in ((128, 1), (512, 1), (2048, 2)):
+        a, la = operand(rng, O.F32, d, d, "c")
+        before = K.launch_count()
+        got, path = gpu_matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)
+        assert path == TENSOR and K.launch_count() - before == launches
+        assert O.rel_err(got, O.matmul(a, a, dot_metadata(la, la), O.F32, is_dot=True)) <= 1e-4
 
 
 def test_aliased_inputs_and_k_zero():
@@ -301,7 +305,9 @@ SPLITK = [
     (256, 8192, 256, O.BF16, O.F32, False, False, 2),     # transposed views of both operands
     (128, 4096, 192, O.F16, O.F16, True, False, 2),
     (128, 16384, 64, O.F8E4M3, O.BF16, True, True, 2),
-    (512, 1024, 768, O.F32, O.F32, True, True, 3),         # config 1: operand split, product, reduction
+    (512, 1024, 768, O.F32, O.F32, True, True, 1),         # config 1: the one-kernel f32 form (K slices added inside the cluster)
+    (512, 1024, 768, O.F32, O.F32, True, False, 1),        # the same with a K-contiguous rhs (a Linear weight view)
+    (256, 16384, 256, O.F32, O.F32, True, True, 3),        # K too long for that form: operand split, product, reduction
     (256, 8192, 250, O.BF16, O.BF16, True, False, 1),      # N not a multiple of 4: runs whole
 ]
 
