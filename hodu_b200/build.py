@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 LIB = os.path.join(LIBDIR, "libhodu_b200.so")
-SOURCES = ["api.cu", "gemm_tc.cu", "gemm_simt.cu", "gemm_f32.cu", "gemm_f32_fused.cu", "relayout.cu", "splitk.cu", "einsum.cu", "conv.cu", "cast.cu", "host_pipeline.cu"]
+SOURCES = ["api.cu", "gemm_tc.cu", "gemm_simt.cu", "gemm_f32.cu", "gemm_f32_fused.cu", "relayout.cu", "splitk.cu", "einsum.cu", "conv.cu", "conv_implicit.cu", "cast.cu", "host_pipeline.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -152,6 +152,10 @@ int run_problem(const Problem& pb, DeviceState* st, cudaStream_t stream);
 // conv2d wire format (validated by the caller) -> im2col + one batched product (conv.cu).
 int run_conv2d(int dtype, const void* input, const void* weight, void* out, const size_t* md, size_t len,
                DeviceState* st, cudaStream_t stream);
+// The same convolution without the unfolded copy (conv_implicit.cu): 0 launched, 1 not a case
+// that form takes (nothing launched), < 0 error.
+int run_conv2d_implicit(int dtype, const void* input, const void* weight, void* out, const size_t* md, DeviceState* st,
+                        cudaStream_t stream, const char** why);
 // Frees the staging memory and streams of the host-buffer forms (host_pipeline.cu).
 void release_host_pipeline(int device);
 // Casts.

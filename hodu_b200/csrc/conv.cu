@@ -178,6 +178,13 @@ int run_conv2d(int dtype, const void* input, const void* weight, void* out, cons
       (W + 2 * pw) * sw >= (1ll << 30))
     return fail(HODU_B200_ERR_INVALID_INPUT, "conv2d: one image (or its unfolded form) exceeds 2^31 elements");
   const bool pointwise = KH == 1 && KW == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && OH == H && OW == W;
+  if (!pointwise && (forced_path() == HODU_B200_PATH_AUTO || forced_path() == HODU_B200_PATH_TENSOR)) {
+    // the implicit form first: no unfolded copy; it declines what it does not take
+    const char* why = "";
+    const int ri = run_conv2d_implicit(dtype, input, weight, out, md, st, stream, &why);
+    if (ri == 0) { set_last_path(HODU_B200_PATH_TENSOR); return 0; }
+    if (ri < 0) return ri;
+  }
   const long long vec = 16 / esize;
   const long long npitch = pointwise ? N : (N + vec - 1) / vec * vec;
 

@@ -172,7 +172,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
         if (!wait_bounded(smem_u32(&tail->raw_free[s]), ph ^ 1u, abort_flag, p.status, code_base | 1u)) break;
         const uint32_t bar = smem_u32(&tail->raw_full[s]);
-        mbar_arrive_expect_tx(bar, kTileA + Cfg::kTileB);
+        mbar_arrive_expect_tx_relaxed(bar, kTileA + Cfg::kTileB);
         const int32_t k0 = static_cast<int32_t>(kb * 32u);
         const uint32_t st = raw_base(s);
         tma_load_2d(st, &map_a, bar, k0, static_cast<int32_t>(m0));

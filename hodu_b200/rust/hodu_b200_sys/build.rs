@@ -8,7 +8,7 @@
 use std::{env, path::PathBuf, process::Command};
 
 const SOURCES: &[&str] = &[
-    "api", "gemm_tc", "gemm_simt", "gemm_f32", "gemm_f32_fused", "relayout", "splitk", "einsum", "conv", "cast", "host_pipeline",
+    "api", "gemm_tc", "gemm_simt", "gemm_f32", "gemm_f32_fused", "relayout", "splitk", "einsum", "conv", "conv_implicit", "cast", "host_pipeline",
 ];
 
 fn main() {

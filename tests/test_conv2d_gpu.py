@@ -43,7 +43,13 @@ CASES = [
     (2, 32, 48, (33, 29), (3, 5), (1, 2), (2, 0), (2, 1), O.F16),       # odd everything, dilation
     (2, 64, 64, (32, 32), (3, 3), (1, 1), (1, 1), (1, 1), O.F32),       # f32 through split TF32
     (1, 2, 3, (5, 5), (3, 3), (1, 1), (0, 0), (1, 1), O.BF16),          # tiny: generic kernel
+    # in_channels a multiple of 64, bf16 / f16: the implicit form (no unfolded copy)
+    (3, 128, 96, (17, 13), (3, 3), (2, 1), (1, 2), (1, 2), O.F16),      # tiles straddle images, odd extents, stride, dilation, ragged Cout
+    (2, 64, 256, (20, 24), (5, 5), (1, 1), (2, 2), (1, 1), O.BF16),     # 5x5, 256-wide channel tiles
+    (40, 64, 64, (9, 9), (3, 3), (1, 1), (0, 0), (1, 1), O.BF16),       # no padding; 1960 pixels: a ragged last tile
+    (2, 192, 64, (31, 31), (3, 3), (3, 3), (1, 1), (1, 1), O.F16),      # three channel blocks, stride 3
 ]
+IMPLICIT = lambda c: c[1] % 64 == 0 and c[8] in (O.BF16, O.F16) and c[4] != (1, 1)
 
 
 @pytest.mark.parametrize("case", CASES, ids=[f"b{c[0]}c{c[1]}-{c[2]}_{c[3][0]}x{c[3][1]}_k{c[4][0]}x{c[4][1]}-{DType(c[8])}" for c in CASES])
@@ -53,11 +59,46 @@ def test_conv2d_vs_oracle(case):
     rng = np.random.default_rng(ci * 7 + co)
     x = O.narrow(rng.standard_normal(b * ci * hw[0] * hw[1]).astype(np.float32), dt)
     w = O.narrow((rng.standard_normal(co * ci * k[0] * k[1]) / np.sqrt(ci * k[0] * k[1])).astype(np.float32), dt)
+    before = K.launch_count()
     got, taken = run_conv(x, w, md, dt)
+    launches = K.launch_count() - before
     want = O.conv2d(x, w, md, dt)
     assert O.rel_err(O.widen(got, dt), O.widen(want, dt)) <= TOL[dt]
-    if b * co * md[8] * md[9] * ci * k[0] * k[1] >= (1 << 24):
+    work = b * co * md[8] * md[9] * ci * k[0] * k[1]
+    if work >= (1 << 24):
         assert taken == K._lib.PATH_TENSOR   # large enough: the tcgen05 kernel, relaid if need be
+        if IMPLICIT(case):
+            assert launches == 2             # re-lay input and weights, then the implicit GEMM: no unfolding pass
+
+
+def test_conv2d_implicit_and_explicit_forms_agree():
+    """The same convolution through both forms (the switch is read once per process, so the
+    explicit form runs in a child process): equal within the bf16 bar, and equal to the oracle."""
+    import subprocess
+    import sys
+    code = r'''
+import sys, numpy as np
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+from test_conv2d_gpu import run_conv
+from hodu_b200.op_metadatas import conv2d_metadata
+from oracle import oracle as O
+md = conv2d_metadata(4, 64, 128, (28, 28), (3, 3), (1, 1), (1, 1), (1, 1))
+rng = np.random.default_rng(1)
+x = O.narrow(rng.standard_normal(4 * 64 * 28 * 28).astype(np.float32), O.BF16)
+w = O.narrow((rng.standard_normal(128 * 64 * 9) / 24).astype(np.float32), O.BF16)
+got, _ = run_conv(x, w, md, O.BF16)
+np.save(sys.argv[1], got)
+''' % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.path.dirname(os.path.abspath(__file__)))
+    import tempfile
+    outs = []
+    for implicit in ("1", "0"):
+        with tempfile.NamedTemporaryFile(suffix=".npy") as f:
+            env = dict(os.environ, HODU_B200_CONV_IMPLICIT=implicit)
+            r = subprocess.run([sys.executable, "-c", code, f.name], capture_output=True, text=True, timeout=600, env=env)
+            assert r.returncode == 0, r.stderr[-2000:]
+            outs.append(np.load(f.name))
+    a, b = (O.widen(o, O.BF16) for o in outs)
+    assert O.rel_err(a, b) <= 1e-2
 
 
 def test_conv2d_argument_errors():
