@@ -117,6 +117,8 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
 // The same, with K cut into slices that run as one batched launch plus a reduction when the
 // output alone cannot occupy the GPU (splitk.cu); otherwise exactly launch_gemm_tc.
 int launch_gemm_tc_splitk(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why);
+// K slices launch_gemm_tc would give `pb` inside ONE launch (clusters of CTAs sharing a tile); 1 = none.
+int tc_planned_k_slices(const Problem& pb, DeviceState* st);
 // Layout front door (relayout.cu): copies the operands TMA cannot describe into scratch as
 // K-contiguous matrices, then runs the tensor-core kernel.  1 = nothing to fix / not applicable.
 bool tc_operand_describable(const Problem& pb, const Operand& op, bool is_lhs, int esize);

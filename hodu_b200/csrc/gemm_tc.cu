@@ -124,6 +124,8 @@ struct TcParams {
   uint32_t k_gen_limit;   // generations of k_gen blocks up to here, then ONE generation for the rest
   uint32_t bdim1, bdim2;  // batch = (b0 * bdim1 + b1) * bdim2 + b2
   uint32_t bk;            // K elements per stage (128 bytes worth)
+  uint32_t k_splits;      // CTAs (or CTA pairs) of a cluster that share one tile, each taking a slice of K
+  uint32_t kb_per_split;  // k-blocks per slice (the last slice takes what is left)
   OperandLoad a, b;
   uint32_t idesc;
   uint32_t out_vec_ok;    // rows of `out` allow 16-byte stores
@@ -366,6 +368,7 @@ template <int BN, bool SWIGLU, bool PAIR, int MH, bool IS_A>
 __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLoad& o,
                                               const CUtensorMap* map0, const CUtensorMap* map1,
                                               SmemTail* tail, uint32_t smem_operand, uint32_t rank,
+                                              uint32_t kb_lo, uint32_t kb_hi,
                                               uint32_t first_tile, uint32_t tile_step,
                                               const TileCoord& first_tc, uint32_t code) {
   using Cfg = TileCfg<BN, PAIR, MH>;
@@ -390,7 +393,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
     if (IS_A) mn0 = static_cast<int32_t>(tc.mt * (PAIR ? 256u * MH : 128u) + rank * 128u * MH);
     else if (PAIR) mn0 = static_cast<int32_t>(SWIGLU ? tc.nt * 128u : tc.nt * 256u + rank * 128u);
     else mn0 = static_cast<int32_t>(tc.nt * kOutCols);
-    for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+    for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
       ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code);
       if (!ok) break;
       const uint32_t bar = full0 + s * 8u;
@@ -432,6 +435,13 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
 //   CTA runs its own epilogue.  Loads are plain per-CTA TMA loads; CTA 0's commits signal
 //   `empty` / `tmem_full` in both CTAs.  With SWIGLU, CTA 0 stages the gate weights and CTA 1
 //   the up weights of the same 128 output columns.
+// p.k_splits > 1 (the one-CTA form without SwiGLU; one tile per cluster): a problem with too few
+//   tiles to occupy the SMs runs as clusters of k_splits CTAs per tile, each taking a
+//   slice of K into its own accumulator.  The slices then share the epilogue: each owns
+//   1/k_splits of the tile's 32-column chunks, writes the chunks it does not own as f32 into its
+//   idle operand ring, and after a cluster barrier adds to its own chunks what the other slices
+//   hold for them, read through distributed shared memory in a fixed order (so the sum does not
+//   depend on timing), and stores them.
 template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
 __global__ void __launch_bounds__(threads_for(MH), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -449,6 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr bool kGenerations = (KIND == KIND_TF32);
   constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
   constexpr uint32_t kTileM = PAIR ? 256u * MH : 128u;
+  constexpr bool kSplitCapable = (!PAIR && !SWIGLU && !kGenerations);   // may run with p.k_splits > 1
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -461,9 +472,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
-  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
-  const uint32_t first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
-  const uint32_t tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
+  // (Forms that never run with K slices keep all of this at its compile-time value.)
+  const uint32_t k_splits = kSplitCapable ? p.k_splits : 1u;
+  const uint32_t crank = (PAIR || kSplitCapable) ? cluster_ctarank() : 0u;   // 0 when launched without clusters
+  const uint32_t rank = PAIR ? crank : 0u;                                   // CTA of the pair
+  const uint32_t slice = kSplitCapable ? crank : 0u;                         // K slice (0 unless k_splits > 1)
+  const uint32_t first_tile = PAIR ? (blockIdx.x >> 1) : (kSplitCapable ? blockIdx.x / k_splits : blockIdx.x);
+  // K slices: exactly one tile per cluster (the slices meet at one cluster barrier).
+  const uint32_t tile_step = PAIR ? (gridDim.x >> 1) : (k_splits > 1u ? p.num_tiles : gridDim.x);
+  uint32_t kb_lo = 0, kb_hi = p.k_blocks;
+  if (k_splits > 1u) {
+    kb_lo = slice * p.kb_per_split;
+    kb_hi = min(kb_lo + p.kb_per_split, p.k_blocks);
+  }
   volatile uint32_t* abort_flag = &tail->abort_flag;
 
   if (threadIdx.x == 0) {
@@ -509,15 +530,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------ producer of A
     if (lane == 0)
-      producer_role<BN, SWIGLU, PAIR, MH, true>(p, p.a, &map_a, &map_a, tail, smem_a, rank, first_tile,
-                                                tile_step, first_tc, code_base | 1u);
+      producer_role<BN, SWIGLU, PAIR, MH, true>(p, p.a, &map_a, &map_a, tail, smem_a, rank, kb_lo, kb_hi,
+                                                first_tile, tile_step, first_tc, code_base | 1u);
     __syncwarp();
   } else if (warp == 6) {
     // ------------------------------------------------------------ producer of B
     if (lane == 0) {
       const CUtensorMap* m0 = (PAIR && SWIGLU && rank == 1) ? &map_b2 : &map_b;
-      producer_role<BN, SWIGLU, PAIR, MH, false>(p, p.b, m0, &map_b2, tail, smem_b, rank, first_tile,
-                                                 tile_step, first_tc, code_base | 5u);
+      producer_role<BN, SWIGLU, PAIR, MH, false>(p, p.b, m0, &map_b2, tail, smem_b, rank, kb_lo, kb_hi,
+                                                 first_tile, tile_step, first_tc, code_base | 5u);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -532,12 +553,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // issuing warp for the second accumulator of the 512x256 form measured no further gain.)
       const uint32_t a_hi = p.a.desc_hi, b_hi = p.b.desc_hi;
       const uint32_t a_step = p.a.kstep16, b_step = p.b.kstep16;
-      const uint32_t a_lo0 = (smem_a >> 4) | p.a.desc_lo, b_lo0 = (smem_b >> 4) | p.b.desc_lo;
-      const uint32_t idesc = p.idesc, k_blocks = p.k_blocks;
+      // (A CTA of a cluster other than rank 0 sees its own shared memory at addresses that carry
+      // the rank above bit 24; the descriptor's address field takes the offset within the CTA.)
+      const uint32_t a_lo0 = ((smem_a & 0x3FFFFu) >> 4) | p.a.desc_lo, b_lo0 = ((smem_b & 0x3FFFFu) >> 4) | p.b.desc_lo;
+      const uint32_t idesc = p.idesc, k_blocks = kb_hi;
       uint32_t a_lo = a_lo0, b_lo = b_lo0;  // descriptor low words of the current stage
       uint32_t full_bar = smem_u32(&tail->full[0]), empty_bar = smem_u32(&tail->empty[0]);
       for (uint32_t t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-      uint32_t kb0 = 0;
+      uint32_t kb0 = kb_lo;
       do {
         // One accumulator generation: the whole tile, or (long f32 products) a run of k_gen
         // k-blocks whose sum the epilogue adds to the output before the next run starts afresh.
@@ -619,6 +642,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         PAIR ? mapa_shared(smem_u32(&tail->tmem_empty[0]), 0u) : smem_u32(&tail->tmem_empty[0]);
     uint32_t lt = 0;
     bool epi_ok = true;
+    [[maybe_unused]] bool split_synced = false;   // this warp has been through the K-slice barrier
     for (uint32_t t = first_tile; epi_ok && t < p.num_tiles; t += tile_step) {
     // Where this tile's rows go: worked out BEFORE the wait for the accumulator (these divisions
     // and 64-bit products measured ~800 cycles, which were exposed after the wait).
@@ -642,6 +666,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!ok) { epi_ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
+      // Scale and bias of chunk c, applied to the finished sums.
+      auto finish_chunk = [&](uint32_t c, uint32_t (&v)[32]) {
+        if constexpr (!SWIGLU && !kIntAcc) {
+          if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
+          }
+          if constexpr (OUT == OUT_F32 || OUT == OUT_BF16 || OUT == OUT_F16) {
+            if (p.bias != nullptr && !later_gen) {  // uniform over the grid; once per output
+              // Lane l fetches the bias of column c*32 + l; the 32 values go round by shuffle.
+              const uint32_t bcol = n0 + c * 32u + lane;
+              const float mine = bcol < p.N ? load_bias<OUT>(p.bias, static_cast<long long>(bcol) * p.bias_stride) : 0.0f;
+              const bool each = (p.bias_flags == HODU_B200_LINEAR_ROUND_EACH_OP);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float x = __uint_as_float(v[j]);
+                if (each) x = round_to_storage<OUT>(x);
+                v[j] = __float_as_uint(x + __shfl_sync(0xFFFFFFFFu, mine, j));
+              }
+            }
+          }
+        }
+      };
       // Loads chunk c of this warp's rows from TMEM and applies the epilogue arithmetic; v then
       // holds the 32 final values (floats, or raw s32).
       auto load_chunk = [&](uint32_t c, uint32_t (&v)[32]) {
@@ -665,29 +712,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           tmem_wait_ld();
-          if constexpr (!kIntAcc) {
-            if (p.alpha != 1.0f) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
-            }
-            if constexpr (OUT == OUT_F32 || OUT == OUT_BF16 || OUT == OUT_F16) {
-              if (p.bias != nullptr && !later_gen) {  // uniform over the grid; once per output
-                // Lane l fetches the bias of column c*32 + l; the 32 values go round by shuffle.
-                const uint32_t bcol = n0 + c * 32u + lane;
-                const float mine = bcol < p.N ? load_bias<OUT>(p.bias, static_cast<long long>(bcol) * p.bias_stride) : 0.0f;
-                const bool each = (p.bias_flags == HODU_B200_LINEAR_ROUND_EACH_OP);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  float x = __uint_as_float(v[j]);
-                  if (each) x = round_to_storage<OUT>(x);
-                  v[j] = __float_as_uint(x + __shfl_sync(0xFFFFFFFFu, mine, j));
-                }
-              }
-            }
-          }
+          finish_chunk(c, v);
         }
       };
       const bool staged = kStaged && (p.out_vec_ok & 1u);  // uniform over the warp
+      // Converts the 32 final values of chunk c and stores them (through the warp's 2 KB staging
+      // buffer when the output rows allow 16-byte stores).
+      auto store_chunk = [&](uint32_t c, uint32_t (&v)[32]) {
+        const uint32_t col = n0 + c * 32u;
+        if (staged) {
+          if constexpr (kStaged) {
+            uint32_t pk[ChunkWords<OUT>::value];
+            pack_chunk<OUT>(v, pk);
+            store_packed_staged<ChunkWords<OUT>::value>(out_tile, p.ldc * osz, row - lane, p.M, col * osz,
+                                                        p.N * osz, pk, stage_buf, lane,
+                                                        OUT == OUT_F32 && later_gen);
+          }
+        } else if (row_ok) {
+          const int ncols = static_cast<int>(min(32u, p.N - col));
+          if constexpr (OUT == OUT_F32 && kGenerations) {
+            if (later_gen) {  // the lane that stored these elements adds the new generation to them
+              const float* old = reinterpret_cast<const float*>(out_row + static_cast<size_t>(c) * 32u * osz);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) v[j] = __float_as_uint(old[j] + __uint_as_float(v[j]));
+            }
+          }
+          store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
+                               (p.out_vec_ok & 1u) != 0u);
+        }
+      };
       // The 512x256 form cannot hide its epilogue behind the next tile, so for 2-byte outputs
       // the warp first pulls ALL its chunks out of TMEM into registers (already packed), hands
       // the accumulator back to the MMA issuer, and only then does the global stores.
@@ -707,7 +761,96 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // converting the next chunk; tails of M and N are clipped by the tensor map.
       bool tail_tma = false;
       if constexpr (kStaged) tail_tma = staged && last_tile && p.out_tma != 0u && !(kGenerations && p.k_gen < p.k_blocks);
-      if (tail_tma) {
+      bool split_tile = false;
+      if constexpr (kSplitCapable) split_tile = k_splits > 1u;
+      if (split_tile) {
+        if constexpr (kSplitCapable) {
+          // K slices of one tile in the CTAs (or pairs) of this cluster: see the kernel's header.
+          static_assert(kChunks * 16384u <= static_cast<uint32_t>(kStages * (kStageA + kStageB)),
+                        "the partial sums of a tile must fit the operand ring");
+          const uint32_t per = kChunks / k_splits;             // chunks each slice owns
+          // A chunk of partial sums (128 rows x 32 columns of f32, 16 KB) lies as eight 2 KB planes,
+          // plane j holding columns 4j..4j+3 of every row, 16 bytes per row: a warp's 32 rows are
+          // 512 contiguous bytes of a plane, both for the local stores and for the reads from
+          // another CTA (which the cluster network serves per contiguous run, not per lane).
+          const uint32_t my_row = (q * 32u + lane) * 16u;
+          auto dump_chunk = [&](uint32_t c, const uint32_t (&v)[32]) {
+            const uint32_t dst = base_u32 + c * 16384u + my_row;
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + j * 2048u), "r"(v[4 * j]),
+                           "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                           : "memory");
+          };
+          // 1. The chunks other slices own: accumulator -> this CTA's idle operand ring.  Two at a
+          // time, so that the TMEM load of one runs under the stores of the other.
+          const uint32_t n_valid = min(kChunks, (p.N - n0 + 31u) / 32u);   // chunks inside N (uniform)
+          const uint32_t own_lo = slice * per, own_hi = own_lo + per;
+          auto foreign = [&](uint32_t i) { return i < own_lo ? i : i + per; };   // i-th chunk not owned
+          const uint32_t n_foreign = n_valid <= own_lo ? n_valid : (n_valid <= own_hi ? own_lo : n_valid - per);
+#pragma unroll 1
+          for (uint32_t i = 0; i < n_foreign; i += 2u) {
+            uint32_t va[32], vb[32];
+            const uint32_t ca = foreign(i), cb = foreign(i + 1u);
+            const bool two = i + 1u < n_foreign;
+            tmem_ld_32x32(t_row + ca * 32u, va);
+            tmem_wait_ld();
+            if (two) tmem_ld_32x32(t_row + cb * 32u, vb);
+            dump_chunk(ca, va);
+            if (two) {
+              tmem_wait_ld();
+              dump_chunk(cb, vb);
+            }
+          }
+          cluster_sync_all();   // every slice's partial sums are in place (and visible cluster-wide)
+          split_synced = true;
+          // 2. The chunks this slice owns: own accumulator plus what the other slices hold, always
+          // added in the same order (own, then the slices after this one, cyclically), three
+          // slices per round of reads.  The first round for the next chunk is issued before the
+          // current chunk is converted and stored.
+          uint4 x[3][8];
+          auto fetch_remote = [&](uint32_t c, uint32_t t0) {   // slices slice + t0 .. slice + t0 + 2
+#pragma unroll
+            for (uint32_t i = 0; i < 3; ++i) {
+              if (t0 + i < k_splits) {
+                const uint32_t s2 = (slice + t0 + i) & (k_splits - 1u);
+                const uint32_t src = mapa_shared(base_u32 + c * 16384u + my_row, s2);
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) x[i][j] = ld_cluster_v4(src + j * 2048u);
+              }
+            }
+          };
+          const uint32_t own_end = min(own_hi, n_valid);
+          if (own_lo < own_end) fetch_remote(own_lo, 1u);
+#pragma unroll 1
+          for (uint32_t c = own_lo; c < own_end; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_row + c * 32u, v);
+            tmem_wait_ld();
+#pragma unroll 1
+            for (uint32_t t0 = 1; t0 < k_splits; t0 += 3u) {
+#pragma unroll
+              for (uint32_t i = 0; i < 3; ++i) {
+                if (t0 + i < k_splits) {
+#pragma unroll
+                  for (uint32_t j = 0; j < 8; ++j) {
+                    const uint32_t w[4] = {x[i][j].x, x[i][j].y, x[i][j].z, x[i][j].w};
+#pragma unroll
+                    for (uint32_t e = 0; e < 4; ++e) {
+                      if constexpr (kIntAcc) v[4 * j + e] += w[e];
+                      else v[4 * j + e] = __float_as_uint(__uint_as_float(v[4 * j + e]) + __uint_as_float(w[e]));
+                    }
+                  }
+                }
+              }
+              if (t0 + 3u < k_splits) fetch_remote(c, t0 + 3u);
+              else if (c + 1u < own_end) fetch_remote(c + 1u, 1u);
+            }
+            finish_chunk(c, v);
+            store_chunk(c, v);
+          }
+        }
+      } else if (tail_tma) {
         if constexpr (kStaged) {
           constexpr uint32_t kWords = ChunkWords<OUT>::value;      // 16 or 32 words per lane and chunk
           constexpr uint32_t kChunkBytes = kWords * 4u * 32u;      // 2 KB or 4 KB
@@ -800,27 +943,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (col >= p.N) break;  // uniform over the warp
           uint32_t v[32];
           load_chunk(c, v);
-          if (staged) {
-            if constexpr (kStaged) {
-              uint32_t pk[ChunkWords<OUT>::value];
-              pack_chunk<OUT>(v, pk);
-              store_packed_staged<ChunkWords<OUT>::value>(out_tile, p.ldc * osz, row - lane, p.M, col * osz,
-                                                          p.N * osz, pk, stage_buf, lane,
-                                                          OUT == OUT_F32 && later_gen);
-            }
-          } else if (row_ok) {
-            const int ncols = static_cast<int>(min(32u, p.N - col));
-            if constexpr (OUT == OUT_F32 && kGenerations) {
-              if (later_gen) {  // the lane that stored these elements adds the new generation to them
-                const float* old = reinterpret_cast<const float*>(out_row + static_cast<size_t>(c) * 32u * osz);
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (j < ncols) v[j] = __float_as_uint(old[j] + __uint_as_float(v[j]));
-              }
-            }
-            store_row_chunk<OUT>(out_row + static_cast<size_t>(c) * 32u * osz, v, ncols,
-                                 (p.out_vec_ok & 1u) != 0u);
-          }
+          store_chunk(c, v);
         }
       }
       if (!released) {
@@ -835,12 +958,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       kb0 = generation_end(p, kb0);
     } while (kGenerations && kb0 < p.k_blocks);
     }
+    if constexpr (kSplitCapable) {
+      // A warp that gave up before the K-slice barrier still owes the cluster its arrival.
+      if (k_splits > 1u && !split_synced) cluster_sync_all();
+    }
+  }
+  if constexpr (kSplitCapable) {
+    // The warps without a share in the epilogue take part in the K-slice barrier here.
+    if (k_splits > 1u && (warp < 2u || warp == 6u)) cluster_sync_all();
   }
 
   // A CTA of a pair may not leave (or free TMEM) while its peer can still read its shared
   // memory, signal its barriers or write its TMEM.
   tc_fence_before_sync();
-  if constexpr (PAIR) cluster_sync_all();   // also a barrier over this CTA's own threads
+  // ... and a K slice not while the others can still read its partial sums.
+  if (PAIR || k_splits > 1u) cluster_sync_all_relaxed();   // also a barrier over this CTA's own threads
   else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
@@ -1090,6 +1222,11 @@ bool build_output_map(const TcParams& p, int osz, uint32_t batches, CUtensorMap*
   return true;
 }
 
+// Clusters of 2, 4 and 8 one-CTA tiles' K slices that can be resident at once, per device
+// (index log2(slices)); 0 = not measured yet.  launch_inst fills it in, the planner reads it.
+std::atomic<int> g_split_capacity[kMaxDevices][4];
+constexpr int kSplitDoesNotFit = -0x5117;   // launch_inst: more tiles than resident clusters, nothing launched
+
 template <int KIND, int BN, int OUT, bool SWIGLU, bool PAIR, int MH>
 int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mo,
                 const TcParams& p, int device, int sm_count, cudaStream_t stream) {
@@ -1099,7 +1236,12 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   static_assert(sizeof(SmemTail) <= 256, "barrier block outgrew its slot");
   // CTAs (1-CTA form) or CTA pairs that can be resident; concurrent first callers compute the
   // same value, so relaxed atomics are enough.
-  static std::atomic<int> max_ctas[kMaxDevices];
+  static std::atomic<int> max_ctas[kMaxDevices][4];   // by log2(K slices)
+  if (p.k_splits != 1u && (PAIR || SWIGLU || KIND == KIND_TF32 || (p.k_splits != 2u && p.k_splits != 4u && p.k_splits != 8u) ||
+                           (BN / 32) % p.k_splits != 0u))
+    return fail(HODU_B200_ERR_LAUNCH, "K slices asked of a tile form that has none");
+  const int split_log2 = p.k_splits >= 8u ? 3 : (p.k_splits >= 4u ? 2 : (p.k_splits == 2u ? 1 : 0));
+  const unsigned cluster_ctas = (PAIR ? 2u : 1u) * p.k_splits;
   auto kern = gemm_tc_kernel<KIND, BN, OUT, SWIGLU, PAIR, MH>;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(threads_for(MH), 1, 1);
@@ -1107,9 +1249,9 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int n_attrs = 0;
-  if (PAIR) {
+  if (cluster_ctas > 1u) {
     attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
-    attrs[n_attrs].val.clusterDim.x = 2; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
+    attrs[n_attrs].val.clusterDim.x = cluster_ctas; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
     ++n_attrs;
   }
   if (dependent_launch_enabled()) {
@@ -1121,26 +1263,29 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   }
   cfg.attrs = attrs;
   cfg.numAttrs = n_attrs;
-  int resident = max_ctas[device].load(std::memory_order_relaxed);
+  int resident = max_ctas[device][split_log2].load(std::memory_order_relaxed);
   if (resident == 0) {
     HODU_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)),
                   HODU_B200_ERR_LAUNCH);
-    int n = PAIR ? sm_count / 2 : sm_count;
-    if (PAIR) {
-      cfg.gridDim = dim3(2, 1, 1);
+    int n = sm_count / static_cast<int>(cluster_ctas);
+    if (cluster_ctas > 1u) {
+      cfg.gridDim = dim3(cluster_ctas, 1, 1);
       int q = 0;
       if (cudaOccupancyMaxActiveClusters(&q, kern, &cfg) == cudaSuccess && q >= 1) n = q;
       else cudaGetLastError();
     }
     resident = n > 0 ? n : 1;
-    max_ctas[device].store(resident, std::memory_order_relaxed);
+    max_ctas[device][split_log2].store(resident, std::memory_order_relaxed);
+    if (!PAIR) g_split_capacity[device][split_log2].store(resident, std::memory_order_relaxed);
   }
+  // K slices meet at a cluster barrier, so every tile's cluster has to be resident at once.
+  if (p.k_splits > 1u && p.num_tiles > static_cast<uint32_t>(resident)) return kSplitDoesNotFit;
   const int units = static_cast<int>(p.num_tiles < static_cast<uint32_t>(resident) ? p.num_tiles : resident);
-  cfg.gridDim = dim3(PAIR ? 2 * units : units, 1, 1);
+  cfg.gridDim = dim3(cluster_ctas * static_cast<unsigned>(units), 1, 1);
   if (debug_enabled())
-    fprintf(stderr, "[hodu_b200] gemm_tc %s: %u tiles of %dx%d, grid %u, %zu B smem, A %s x%u, B %s x%u%s\n",
-            PAIR ? "pair" : "1-CTA", p.num_tiles, PAIR ? 256 * MH : 128, SWIGLU ? BN / 2 : BN, cfg.gridDim.x, smem,
+    fprintf(stderr, "[hodu_b200] gemm_tc %s: %u tiles of %dx%d, %u K slice(s), grid %u, %zu B smem, A %s x%u, B %s x%u%s\n",
+            PAIR ? "pair" : "1-CTA", p.num_tiles, PAIR ? 256 * MH : 128, SWIGLU ? BN / 2 : BN, p.k_splits, cfg.gridDim.x, smem,
             p.a.mn_major ? "M-major" : "K-major", p.a.boxes, p.b.mn_major ? "N-major" : "K-major", p.b.boxes,
             p.b.slab_dim ? " (slab dim)" : "");
   if (debug_enabled()) {
@@ -1162,7 +1307,13 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     else if (p.num_tiles % (p.tiles_m * p.tiles_n) != 0) bad = "tile count is not batches x tiles_m x tiles_n";
     else if (p.ldc < p.N || p.out_batch_stride < static_cast<unsigned long long>(p.M - 1) * p.ldc + p.N) bad = "output rows or batches overlap";
     else if (p.k_gen == 0 || p.k_gen > p.k_blocks || p.k_gen_limit > p.k_blocks) bad = "accumulator generations out of range";
-    else if (cfg.gridDim.x == 0 || (PAIR && (cfg.gridDim.x & 1u))) bad = "grid size";
+    else if (cfg.gridDim.x == 0 || cfg.gridDim.x % cluster_ctas != 0u) bad = "grid size";
+    else if (p.k_splits != 1u && p.k_splits != 2u && p.k_splits != 4u && p.k_splits != 8u) bad = "K slices not 1, 2, 4 or 8";
+    else if (p.k_splits > 1u && (PAIR || SWIGLU || KIND == KIND_TF32 || cluster_ctas > 8u || (BN / 32) % p.k_splits != 0u ||
+                                 cfg.gridDim.x != cluster_ctas * p.num_tiles ||
+                                 static_cast<uint64_t>(p.kb_per_split) * (p.k_splits - 1u) >= p.k_blocks ||
+                                 static_cast<uint64_t>(p.kb_per_split) * p.k_splits < p.k_blocks))
+      bad = "K slices do not fit this form, this grid or K";
     else if (smem > 232448) bad = "shared memory beyond the 227 KB a CTA can have";
     if (bad) return fail(HODU_B200_ERR_LAUNCH, "debug check before launch: %s", bad);
   }
@@ -1216,7 +1367,31 @@ bool tc_operand_describable(const Problem& pb, const Operand& op, bool is_lhs, i
   return true;
 }
 
+namespace {
+// Plans and launches; with `plan_only` it stops after the plan and reports the K slices chosen.
+int launch_gemm_tc_planned(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why, bool allow_split,
+                           int* plan_only);
+}
+
+int tc_planned_k_slices(const Problem& pb, DeviceState* st) {
+  const char* why = nullptr;
+  int slices = 1;
+  if (launch_gemm_tc_planned(pb, st, nullptr, &why, true, &slices) != 0) return 1;
+  return slices;
+}
+
 int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
+  // A plan with K slices assumes how many clusters fit the device; the first launch of each
+  // cluster size measures it, and when the plan then does not fit it is made again without.
+  int rc = launch_gemm_tc_planned(pb, st, stream, why, true, nullptr);
+  if (rc == kSplitDoesNotFit) rc = launch_gemm_tc_planned(pb, st, stream, why, true, nullptr);
+  if (rc == kSplitDoesNotFit) rc = launch_gemm_tc_planned(pb, st, stream, why, false, nullptr);
+  return rc;
+}
+
+namespace {
+int launch_gemm_tc_planned(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why, bool allow_split,
+                           int* plan_only) {
   static const char* none = "";
   *why = none;
   int kind, esize, fmt;
@@ -1251,7 +1426,13 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   const int forced = forced_path();
   const int units_pair = st->sm_count / 2 > 0 ? st->sm_count / 2 : 1;
   const double k_blocks_d = static_cast<double>((pb.K + (128 / esize) - 1) / (128 / esize));
-  int form = 0, bn = 256;
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= kMaxDevices) device = 0;
+  // HODU_B200_KSPLIT: 1 = never slice K across a cluster, 2 / 4 / 8 = that many slices whenever
+  // a form allows it (tuning aid); unset or 0 = by estimated time.
+  static const int split_forced = [] { const char* e = getenv("HODU_B200_KSPLIT"); return e ? atoi(e) : 0; }();
+  int form = 0, bn = 256, splits = 1;
   {
     double best = 1e300;
     auto consider = [&](int f, int c) {
@@ -1285,7 +1466,40 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
         if (!(b_cls == 1 && esize == 1)) consider(0, 64);
       }
     }
+    // K slices across a cluster, when the tiles chosen above leave SMs idle: decided on a second
+    // estimate, fitted to launches of few tiles (cycles at the clock such launches run at):
+    //   5200 per launch (set-up, first loads, teardown); per k-block 590 / 630 / 680 for one CTA
+    //   with 64 / 128 / 256 columns, 620 per CTA of a 256 x 256 pair, 1110 of a 512 x 256 pair;
+    //   590 (800 for 4-byte outputs) per 32-column chunk drained and stored; with slices, 285
+    //   per chunk handed to another slice, 700 for the barrier, 700 per chunk read from another.
+    if (allow_split && split_forced != 1 && !only_pair && !pb.swiglu && kind != KIND_TF32) {
+      const double chunk_clk = dtype_size(pb.out_dtype) == 4 ? 800.0 : 590.0;
+      auto kblock_fit = [](int f, int c) { return f == 2 ? 1110.0 : (f == 1 ? 620.0 : (c == 256 ? 680.0 : (c == 128 ? 630.0 : 590.0))); };
+      const int64_t tm0 = form == 2 ? 512 : (form == 1 ? 256 : 128);
+      const int64_t tiles0 = ((pb.M + tm0 - 1) / tm0) * ((pb.N + bn - 1) / bn) * pb.batches;
+      const int64_t units0 = form ? units_pair : st->sm_count;
+      const double whole = 5200.0 + static_cast<double>((tiles0 + units0 - 1) / units0) * k_blocks_d * kblock_fit(form, bn) +
+                           (bn / 32) * (form == 2 ? 2 : 1) * chunk_clk;
+      double best_split = 1e300;
+      int split_bn = 0, split_ks = 1;
+      for (int ks = 2; ks <= 8; ks *= 2) {
+        if (split_forced > 1 && split_forced != ks) continue;
+        for (int c = 256; c >= 64; c /= 2) {
+          if ((c / 32) % ks != 0 || (c == 64 && b_cls == 1 && esize == 1)) continue;
+          const int64_t tiles = ((pb.M + 127) / 128) * ((pb.N + c - 1) / c) * pb.batches;
+          const int measured = g_split_capacity[device][ks == 8 ? 3 : (ks == 4 ? 2 : 1)].load(std::memory_order_relaxed);
+          const int64_t capacity = measured > 0 ? measured : st->sm_count / ks;
+          if (tiles > capacity || k_blocks_d < 4.0 * ks) continue;   // all clusters resident; >= 4 k-blocks a slice
+          const int chunks = c / 32, per = chunks / ks;
+          const double t = 5200.0 + static_cast<double>((static_cast<int64_t>(k_blocks_d) + ks - 1) / ks) * kblock_fit(0, c) +
+                           (chunks - per) * 285.0 + 700.0 + per * (chunk_clk + (ks - 1) * 700.0);
+          if (t < best_split) { best_split = t; split_bn = c; split_ks = ks; }
+        }
+      }
+      if (split_ks > 1 && (split_forced > 1 || best_split < 0.93 * whole)) { form = 0; bn = split_bn; splits = split_ks; }
+    }
   }
+  if (plan_only) { *plan_only = splits; return 0; }
   const bool use_pair = form != 0;
   const int mh = form == 2 ? 2 : 1;
   const int64_t tile_m = form == 2 ? 512 : (form == 1 ? 256 : BM);
@@ -1326,6 +1540,12 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   p.num_tiles = static_cast<uint32_t>(num_tiles);
   p.bk = 128u / esize;
   p.k_blocks = static_cast<uint32_t>((pb.K + p.bk - 1) / p.bk);
+  p.k_splits = static_cast<uint32_t>(splits);
+  p.kb_per_split = (p.k_blocks + p.k_splits - 1u) / p.k_splits;
+  if (p.k_splits > 1u && static_cast<uint64_t>(p.kb_per_split) * (p.k_splits - 1u) >= p.k_blocks) {
+    p.k_splits = 1u;   // the last slice would be empty
+    p.kb_per_split = p.k_blocks;
+  }
   // Rows of A per raster group: 4096 in the 512x256 form (measured on the 8192^3 and MLP shapes:
   // 2048 and 8192 rows are 1-2 % slower, 16384 rows 10 % slower), 2048 in the others.
   p.group_m = form == 2 ? 8 : (form == 1 ? 8 : 16);
@@ -1391,9 +1611,6 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   if (kind == KIND_TF32 && pb.f32_presplit && !pb.swiglu && p.k_blocks > 128u)
     p.k_gen = p.k_blocks > 3072u ? 64u : 128u;
 
-  int device = 0;
-  cudaGetDevice(&device);
-
   // The output's own tensor map, when it has one (HODU_B200_TMA_STORE=0 keeps ordinary stores).
   CUtensorMap out_map;
   memset(&out_map, 0, sizeof(out_map));
@@ -1428,5 +1645,6 @@ int launch_gemm_tc(const Problem& pb, DeviceState* st, cudaStream_t stream, cons
   *why = "output dtype has no tensor-core epilogue";
   return 1;
 }
+}  // namespace
 
 }  // namespace hodu_b200

@@ -101,7 +101,7 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
-// Tiled 5-D load global -> this CTA's shared memory, completion on an mbarrier.
+// Tiled 5-D load global -> this CTA's shared memory, completion on an mbarrier of this CTA.
 // c0 is the innermost coordinate; c0 * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int32_t c0, int32_t c1, int32_t c2, int32_t c3,
@@ -154,6 +154,15 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
   return r;
+}
+// 16 bytes of another CTA's shared memory (shared::cluster address from mapa_shared).
+__device__ __forceinline__ uint4 ld_cluster_v4(uint32_t cluster_addr) {
+  uint4 v;
+  asm volatile("ld.shared::cluster.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
 }
 // Arrive (+ expected transaction bytes) on an mbarrier given by a shared::cluster address.
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
@@ -339,6 +348,12 @@ __device__ __forceinline__ void cluster_wait() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
                ::: "memory");
+}
+// The same barrier without memory ordering: for a rendezvous that only has to keep a CTA (its
+// shared memory, its barriers, its TMEM) alive until its peers are done with it.  The release
+// form would first wait for every global store of the arriving thread to complete.
+__device__ __forceinline__ void cluster_sync_all_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
 }
 
 }  // namespace ptx

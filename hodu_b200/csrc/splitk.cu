@@ -103,6 +103,13 @@ int pick_splits(const Problem& pb, const DeviceState* st) {
 int launch_gemm_tc_splitk(const Problem& pb, DeviceState* st, cudaStream_t stream, const char** why) {
   const int splits = forced_path() == HODU_B200_PATH_AUTO || forced_path() == HODU_B200_PATH_TENSOR ? pick_splits(pb, st) : 1;
   if (splits <= 1) return launch_gemm_tc(pb, st, stream, why);
+  // The tensor-core kernel can slice K itself, across the CTAs of a cluster and without scratch
+  // or a second launch; where its planner would, that is the faster of the two.
+  // (Measured exception: a K so long that the cluster's slices would still be 32 k-blocks or more
+  // while this path has twice as many slices -- 256 x 8192 x 2048 -- stays here.)
+  const int in_kernel = tc_planned_k_slices(pb, st);
+  const long long k_blocks = pb.K * dtype_size(pb.in_dtype) / 128;
+  if (in_kernel > 1 && !(splits >= 2 * in_kernel && k_blocks / in_kernel >= 32)) return launch_gemm_tc(pb, st, stream, why);
   Problem q = pb;
   q.K = pb.K / splits;
   q.batch_ndim = 1;

@@ -301,10 +301,12 @@ def test_saturation_of_e4m3_output():
 # ---------------------------------------------------------------- split over K for small outputs
 SPLITK = [
     # M, K, N, in dtype, out dtype, lhs K-contiguous?, rhs N-contiguous?, launches expected
-    (256, 8192, 256, O.BF16, O.BF16, True, True, 2),
-    (256, 8192, 256, O.BF16, O.F32, False, False, 2),     # transposed views of both operands
-    (128, 4096, 192, O.F16, O.F16, True, False, 2),
-    (128, 16384, 64, O.F8E4M3, O.BF16, True, True, 2),
+    # (one launch: K slices across the CTAs of a cluster; two: slices as batches plus a reduction)
+    (256, 8192, 256, O.BF16, O.BF16, True, True, 1),
+    (256, 8192, 256, O.BF16, O.F32, False, False, 1),     # transposed views of both operands
+    (128, 4096, 192, O.F16, O.F16, True, False, 1),
+    (128, 16384, 64, O.F8E4M3, O.BF16, True, True, 1),
+    (256, 8192, 2048, O.BF16, O.BF16, True, True, 2),     # K long enough for eight slices of 16 k-blocks
     (512, 1024, 768, O.F32, O.F32, True, True, 1),         # config 1: the one-kernel f32 form (K slices added inside the cluster)
     (512, 1024, 768, O.F32, O.F32, True, False, 1),        # the same with a K-contiguous rhs (a Linear weight view)
     (256, 16384, 256, O.F32, O.F32, True, True, 3),        # K too long for that form: operand split, product, reduction
