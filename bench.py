@@ -56,6 +56,7 @@ WIDENED = {
     "linear": "Linear with bias, X[8192,4096] . W[4096,4096]^T + b[4096], bf16 (hodu_nn::Linear forward, one launch)",
     "einsum_qk": "einsum bhqd,bhkd->bhqk, b=4 h=16 q=k=2048 d=128, bf16 (attention scores; 512 MiB written: HBM-bound)",
     "conv3x3": "conv2d NCHW batch 32, 64->64 channels, 56x56, 3x3, padding 1, bf16",
+    "proj": "bf16 matmul X[1024,4096] . W[4096,1024] (a projection on 1024 tokens: 32 output tiles, K slices inside one launch)",
 }
 WORKLOADS.update(WIDENED)
 CAST_WORKLOADS = {"cast_bf16": ("bf16", 2), "cast_e4m3": ("f8e4m3", 1)}  # destination dtype, its size
@@ -75,7 +76,7 @@ NCU_TRAFFIC = {
 }
 NCU_TRAFFIC_KERNEL_SHA = "d3aff341288f"   # kernel_sources_sha() at the time of the captures above
 NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0,
-                       "linear": 2250.0, "einsum_qk": 2250.0, "conv3x3": 2250.0}
+                       "linear": 2250.0, "einsum_qk": 2250.0, "conv3x3": 2250.0, "proj": 2250.0}
 SUB_CONFIGS_1GPU = ["c1", "c3", "c4", "c5", "cast_bf16", "cast_e4m3"]
 SUB_CONFIGS_SHARDED = ["c3", "c4", "c5"]     # config 1 does not shard (replicas only); casts are input preparation
 MIN_REGION_MS = 50.0
@@ -209,7 +210,8 @@ def cpu_reference_rate(workload: str, budget_s: float):
         # the widened rows are timed as the f32 product of their GEMM shape (the reference's CPU
         # conv2d / einsum kernels are scalar loops; its OpenBLAS build unfolds and calls sgemm too)
         shapes = {"c1": (512, 1024, 768), "c3": (8192, 8192, 8192), "c4": (8192, 8192, 8192), "c5": (16384, 4096, 14336),
-                  "linear": (8192, 4096, 4096), "einsum_qk": (2048, 128, 2048), "conv3x3": (64, 576, 3136)}
+                  "linear": (8192, 4096, 4096), "einsum_qk": (2048, 128, 2048), "conv3x3": (64, 576, 3136),
+                  "proj": (1024, 4096, 1024)}
         m, k, n = shapes[workload]
         b = rng.standard_normal((k, n), dtype=np.float32)
         probe_rows = min(m, 512)
@@ -408,6 +410,18 @@ class Workload:
             self.layer = Linear(w, bias)
             self.flops, self.dtype, self.launches = 2.0 * m * n * k, "bf16", 1
             self.step = lambda: self.layer.forward(x)
+        elif name == "proj":
+            g = torch.Generator(device=dev).manual_seed(14)
+            m, k, n = 1024, 4096, 1024
+            self.a = (torch.randn(m * k, generator=g, device=dev) / 8).bfloat16()
+            self.b = (torch.randn(k * n, generator=g, device=dev) / 8).bfloat16()
+            self.out = torch.empty(m * n, dtype=torch.bfloat16, device=dev)
+            self.md = dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n)))
+            self.flops, self.dtype, self.launches = 2.0 * m * n * k, "bf16", 1
+            # the wrapper's own call, output allocated once: a 15 us product would otherwise be
+            # timed at the rate Python allocates tensors
+            self.step = lambda: K.call_ops_dot(K.dot.BF16, d0, self.a.data_ptr(), self.b.data_ptr(),
+                                               self.out.data_ptr(), self.md, stream_ptr)
         elif name == "einsum_qk":
             from hodu_b200.tensor import einsum
             g = torch.Generator(device=dev).manual_seed(12)

@@ -336,8 +336,10 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (uint32_t j = 0; j < ncols; ++j) dst[j] = o[j];
     }
   }
-  // No CTA may leave while a peer can still read its shared memory.
-  cluster_sync_all();
+  // No CTA may leave while a peer can still read its shared memory.  (A rendezvous only: every
+  // remote read above has delivered its value before its thread arrives, and nothing is published
+  // here, so the arrive carries no release fence -- which would wait for the global stores.)
+  cluster_sync_all_relaxed();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
