@@ -62,19 +62,21 @@ WORKLOADS.update(WIDENED)
 CAST_WORKLOADS = {"cast_bf16": ("bf16", 2), "cast_e4m3": ("f8e4m3", 1)}  # destination dtype, its size
 CAST_ELEMS = 67_108_864
 # DRAM bytes per launch of the dominant kernel, from the ncu captures summarised in profiles/
-# (None until a capture of that workload exists), with the hash of the kernel sources the capture
-# was made from: the line says whether the sources have changed since.
+# (None until a capture of that workload exists): bytes, the summary, the kernel's source file and
+# the hash that file had when the capture was made -- the line says whether it has changed since.
+_PAIR512 = "profiles/gemm_tc_pair512_tma_tail_configs2_3_4_5.md"
+_CAST = "profiles/cast_contig_f32_to_bf16_e4m3_67M_elements.md"
 NCU_TRAFFIC = {
-    "c2": (419.0e6, "profiles/gemm_tc_pair512_tma_tail_configs2_3_4_5.md"),
-    "c3": (492.6e6, "profiles/gemm_tc_pair512_tma_tail_configs2_3_4_5.md"),
-    "c4": (627.2e6, "profiles/gemm_tc_pair512_tma_tail_configs2_3_4_5.md"),
-    "c5": (3921.0e6, "profiles/gemm_tc_pair512_tma_tail_configs2_3_4_5.md"),   # the SwiGLU launch (the dominant one), 2774 + 1147 MB
-    "c1": (5.27e6, "profiles/gemm_f32_fused_config1.md"),
-    "conv3x3": (12.94e6, "profiles/conv_implicit_3x3_64ch_56x56_batch32.md"),   # the GEMM launch; the re-laying pass reads the same again
-    "cast_bf16": (365.0e6, "profiles/cast_contig_f32_to_bf16_e4m3_67M_elements.md"),
-    "cast_e4m3": (312.0e6, "profiles/cast_contig_f32_to_bf16_e4m3_67M_elements.md"),
+    "c2": (409.7e6, _PAIR512, "gemm_tc.cu", "c5146d975cbe"),
+    "c3": (496.7e6, _PAIR512, "gemm_tc.cu", "c5146d975cbe"),
+    "c4": (630.5e6, _PAIR512, "gemm_tc.cu", "c5146d975cbe"),
+    "c5": (3729.0e6, _PAIR512, "gemm_tc.cu", "c5146d975cbe"),   # the SwiGLU launch (the dominant one)
+    "c1": (5.27e6, "profiles/gemm_f32_fused_config1.md", "gemm_f32_fused.cu", "a4a8d29dea22"),
+    "proj": (16.85e6, "profiles/gemm_tc_1cta_k_slices_projection_1024x4096x1024.md", "gemm_tc.cu", "c5146d975cbe"),
+    "conv3x3": (12.94e6, "profiles/conv_implicit_3x3_64ch_56x56_batch32.md", "conv_implicit.cu", "4239b7ec434b"),   # the GEMM launch
+    "cast_bf16": (365.0e6, _CAST, "cast.cu", "ad49356b90fe"),
+    "cast_e4m3": (312.0e6, _CAST, "cast.cu", "ad49356b90fe"),
 }
-NCU_TRAFFIC_KERNEL_SHA = "d3aff341288f"   # kernel_sources_sha() at the time of the captures above
 NOMINAL_PEAK_TFLOPS = {"c1": 1100.0, "c2": 2250.0, "c3": 4500.0, "c4": 4500.0, "c5": 2250.0,
                        "linear": 2250.0, "einsum_qk": 2250.0, "conv3x3": 2250.0, "proj": 2250.0}
 SUB_CONFIGS_1GPU = ["c1", "c3", "c4", "c5", "cast_bf16", "cast_e4m3"]
@@ -82,13 +84,9 @@ SUB_CONFIGS_SHARDED = ["c3", "c4", "c5"]     # config 1 does not shard (replicas
 MIN_REGION_MS = 50.0
 
 
-def kernel_sources_sha() -> str:
-    h = hashlib.sha256()
-    for f in ("gemm_tc.cu", "sm100_ptx.cuh", "cast.cu"):
-        p = os.path.join(ROOT, "hodu_b200", "csrc", f)
-        if os.path.exists(p):
-            h.update(open(p, "rb").read())
-    return h.hexdigest()[:12]
+def kernel_source_sha(file_name: str) -> str:
+    p = os.path.join(ROOT, "hodu_b200", "csrc", file_name)
+    return hashlib.sha256(open(p, "rb").read()).hexdigest()[:12] if os.path.exists(p) else "missing"
 
 
 def measured_peaks():
@@ -594,14 +592,14 @@ def roofline_of(name, wl, ms_step, timed_s, clk, peaks):
     achieved = wl.flops / (ms_step * 1e-3) / per_unit
     if hbm_bound and not is_cast:   # a product whose algorithmic bytes, not flops, bound it
         achieved = wl.alg_bytes / (ms_step * 1e-3) / 1e9
-    traffic, traffic_src = NCU_TRAFFIC.get(name, (None, None))
+    traffic, traffic_src, kernel_file, sha_then = NCU_TRAFFIC.get(name, (None, None, None, None))
     r = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if hbm_bound else "TFLOP/s",
          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src}
     if traffic is not None:
-        sha = kernel_sources_sha()
+        sha = kernel_source_sha(kernel_file)
         r["traffic_source"] = traffic_src
-        r["traffic_kernel_sha"] = {"captured": NCU_TRAFFIC_KERNEL_SHA, "now": sha,
-                                   "kernel_changed_since_capture": sha != NCU_TRAFFIC_KERNEL_SHA}
+        r["traffic_kernel_sha"] = {"file": kernel_file, "captured": sha_then, "now": sha,
+                                   "kernel_changed_since_capture": sha != sha_then}
     if not hbm_bound:
         r["frac_of_nominal"] = achieved / NOMINAL_PEAK_TFLOPS[name]
     else:
