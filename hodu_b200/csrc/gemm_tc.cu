@@ -972,7 +972,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // memory, signal its barriers or write its TMEM.
   tc_fence_before_sync();
   // ... and a K slice not while the others can still read its partial sums.
-  if (PAIR || k_splits > 1u) cluster_sync_all_relaxed();   // also a barrier over this CTA's own threads
+  // (A pair keeps the release form: its last remote mbarrier arrive must have landed before the
+  // peer's shared memory can pass to another CTA.  K slices only READ each other's memory, and
+  // every read has delivered its value before its thread arrives, so they meet without the
+  // fence, which would first wait for the CTA's global stores to complete.)
+  if constexpr (PAIR) cluster_sync_all();   // also a barrier over this CTA's own threads
+  else if (k_splits > 1u) cluster_sync_all_relaxed();
   else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
