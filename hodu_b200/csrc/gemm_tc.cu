@@ -85,9 +85,17 @@ enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_I32 = 4, 
 // Stage ring per CTA.  PAIR: each CTA of the pair stages 128 columns of B.  MH = M-halves
 // (128-row accumulators) per CTA: 1, or 2 for the 512 x 256 pair tile.
 template <int BN, bool PAIR, int MH> struct TileCfg {
-  static constexpr int kStageA = MH * kHalfA;
-  static constexpr int kStageB = PAIR ? 128 * 128 : BN * 128;
-  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 6) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  // k-blocks (128 bytes of K) per stage.  One wait on `full`, one commit to `empty` and one
+  // producer iteration cost the issuing threads ~250 cycles each whatever the stage holds (an
+  // mbarrier probe answers after ~200 cycles even when the phase is long complete), which is more
+  // than the 128 or 256 MMA cycles of a k-block of the narrow one-CTA tiles: those stage two
+  // k-blocks at a time and pay the handshake once for both.
+  static constexpr int kKbPerStage = (!PAIR && BN <= 128) ? 2 : 1;
+  static constexpr int kStageA1 = MH * kHalfA;                    // one k-block
+  static constexpr int kStageB1 = PAIR ? 128 * 128 : BN * 128;
+  static constexpr int kStageA = kKbPerStage * kStageA1;
+  static constexpr int kStageB = kKbPerStage * kStageB1;
+  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 6) : (BN == 256 ? 4 : (BN == 128 ? 3 : 4));
   static constexpr int kEpiWarps = 4 * MH * (MH == 2 ? 2 : 1);
   static constexpr int kEpiStage = 2048;  // per epilogue warp: a 32-row x 64-byte block
   static constexpr int kTmemCols = 2 * BN;  // two accumulators: double buffer (MH 1) or the two halves (MH 2)
@@ -374,6 +382,8 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
   using Cfg = TileCfg<BN, PAIR, MH>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kStageBytes = IS_A ? Cfg::kStageA : Cfg::kStageB;
+  constexpr uint32_t kKbBytes = IS_A ? Cfg::kStageA1 : Cfg::kStageB1;    // one k-block of this operand
+  constexpr uint32_t kKbPerStage = Cfg::kKbPerStage;
   constexpr uint32_t kOutCols = SWIGLU ? BN / 2 : BN;
   volatile uint32_t* abort_flag = &tail->abort_flag;
   const uint32_t my_bytes = o.boxes * o.box_bytes;
@@ -393,14 +403,18 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
     if (IS_A) mn0 = static_cast<int32_t>(tc.mt * (PAIR ? 256u * MH : 128u) + rank * 128u * MH);
     else if (PAIR) mn0 = static_cast<int32_t>(SWIGLU ? tc.nt * 128u : tc.nt * 256u + rank * 128u);
     else mn0 = static_cast<int32_t>(tc.nt * kOutCols);
-    for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
+    for (uint32_t kb = kb_lo; kb < kb_hi; kb += kKbPerStage) {
       ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code);
       if (!ok) break;
       const uint32_t bar = full0 + s * 8u;
-      if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes);
+      const uint32_t n_kb = kKbPerStage == 1u ? 1u : min(kKbPerStage, kb_hi - kb);   // k-blocks this stage holds
+      if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes * n_kb);
       else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes);
-      const int32_t k0 = static_cast<int32_t>(kb * p.bk);
-      uint32_t dst = smem_operand + s * kStageBytes;
+#pragma unroll
+      for (uint32_t j = 0; j < kKbPerStage; ++j) {
+      if (j >= n_kb) break;
+      const int32_t k0 = static_cast<int32_t>((kb + j) * p.bk);
+      uint32_t dst = smem_operand + s * kStageBytes + j * kKbBytes;
       for (uint32_t i = 0; i < o.boxes; ++i, dst += o.box_bytes) {
         const CUtensorMap* mp = map0;
         uint32_t j = i;
@@ -412,6 +426,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
         else { c0 = 0; c1 = k0; c2 = mn / static_cast<int32_t>(o.inner); c3 = c_b2; c4 = c_b1; }
         if (PAIR) tma_load_5d_pair(dst, mp, bar, c0, c1, c2, c3, c4);
         else tma_load_5d(dst, mp, bar, c0, c1, c2, c3, c4);
+      }
       }
       ++issued;
       if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -570,7 +585,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t acc_ph = MH == 2 ? (lt & 1u) : ((lt >> 1) & 1u);
         const uint32_t d_tmem = tmem_base + acc * BN;
         const uint32_t kb_end = kGenerations ? generation_end(p, kb0) : k_blocks;
-        for (uint32_t kb = kb0; kb < kb_end; ++kb) {
+        for (uint32_t kb = kb0; kb < kb_end; kb += Cfg::kKbPerStage) {
           ok = wait_bounded(full_bar, ph, abort_flag, p.status, code_base | 3u);
           if (!ok) break;
           tc_fence_after_sync();
@@ -592,6 +607,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             umma_x4<KIND, CG>(d_tmem, a_lo, a_hi, a_step, b_lo, b_hi, b_step, idesc, 1u);
             if constexpr (MH == 2)
               umma_x4<KIND, CG>(d_tmem + BN, a_lo + (kHalfA >> 4), a_hi, a_step, b_lo, b_hi, b_step, idesc, 1u);
+          }
+          if constexpr (Cfg::kKbPerStage == 2) {   // the stage's second k-block (absent at an odd end of K)
+            if (kb + 1u < kb_end)
+              umma_x4<KIND, CG>(d_tmem, a_lo + (Cfg::kStageA1 >> 4), a_hi, a_step, b_lo + (Cfg::kStageB1 >> 4), b_hi, b_step, idesc, 1u);
           }
           // frees the stage (in both CTAs of a pair) when these MMAs retire
           if constexpr (PAIR) umma_commit_2cta(empty_bar, 3);
@@ -1297,8 +1316,10 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     // Everything the kernel takes on trust, checked on the host before it runs.
     constexpr uint32_t kTileRows = PAIR ? 256u * MH : 128u, kTileCols = SWIGLU ? BN / 2 : BN;
     const char* bad = nullptr;
-    if (p.a.boxes * p.a.box_bytes != static_cast<uint32_t>(Cfg::kStageA)) bad = "lhs boxes do not fill a stage";
-    else if (p.b.boxes * p.b.box_bytes != static_cast<uint32_t>(Cfg::kStageB)) bad = "rhs boxes do not fill a stage";
+    if (p.a.boxes * p.a.box_bytes != static_cast<uint32_t>(Cfg::kStageA1)) bad = "lhs boxes do not fill a k-block of a stage";
+    else if (p.b.boxes * p.b.box_bytes != static_cast<uint32_t>(Cfg::kStageB1)) bad = "rhs boxes do not fill a k-block of a stage";
+    else if (Cfg::kKbPerStage == 2 && KIND == KIND_TF32 && ((p.k_gen & 1u) || (p.k_gen_limit & 1u)) && p.k_gen < p.k_blocks)
+      bad = "accumulator generations must start at even k-blocks when a stage holds two";
     else if (Cfg::kTmemCols > 512 || (Cfg::kTmemCols & (Cfg::kTmemCols - 1)) != 0) bad = "TMEM columns not a power of two <= 512";
     else if (static_cast<uint64_t>(p.tiles_m) * kTileRows < p.M || static_cast<uint64_t>(p.tiles_m - 1) * kTileRows >= p.M)
       bad = "row tiles do not cover M exactly";
@@ -1473,13 +1494,13 @@ int launch_gemm_tc_planned(const Problem& pb, DeviceState* st, cudaStream_t stre
     }
     // K slices across a cluster, when the tiles chosen above leave SMs idle: decided on a second
     // estimate, fitted to launches of few tiles (cycles at the clock such launches run at):
-    //   5200 per launch (set-up, first loads, teardown); per k-block 590 / 630 / 680 for one CTA
+    //   5200 per launch (set-up, first loads, teardown); per k-block 460 / 570 / 680 for one CTA
     //   with 64 / 128 / 256 columns, 620 per CTA of a 256 x 256 pair, 1110 of a 512 x 256 pair;
     //   590 (800 for 4-byte outputs) per 32-column chunk drained and stored; with slices, 285
     //   per chunk handed to another slice, 700 for the barrier, 700 per chunk read from another.
     if (allow_split && split_forced != 1 && !only_pair && !pb.swiglu && kind != KIND_TF32) {
       const double chunk_clk = dtype_size(pb.out_dtype) == 4 ? 800.0 : 590.0;
-      auto kblock_fit = [](int f, int c) { return f == 2 ? 1110.0 : (f == 1 ? 620.0 : (c == 256 ? 680.0 : (c == 128 ? 630.0 : 590.0))); };
+      auto kblock_fit = [](int f, int c) { return f == 2 ? 1110.0 : (f == 1 ? 620.0 : (c == 256 ? 680.0 : (c == 128 ? 570.0 : 460.0))); };
       const int64_t tm0 = form == 2 ? 512 : (form == 1 ? 256 : 128);
       const int64_t tiles0 = ((pb.M + tm0 - 1) / tm0) * ((pb.N + bn - 1) / bn) * pb.batches;
       const int64_t units0 = form ? units_pair : st->sm_count;

@@ -26,7 +26,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CASES = [
     # M, K, N, batches, in dtype, out dtype, lhs K-contiguous?, rhs N-contiguous?
     (512, 2048, 512, 0, O.BF16, O.BF16, True, True),
-    (1536, 1536, 1536, 0, O.BF16, O.BF16, True, True),      # 72 tiles of 128 x 256, two slices
+    (1024, 4096, 1024, 0, O.BF16, O.BF16, True, True),      # 32 tiles of 128 x 256, four slices
+    (1536, 1536, 1536, 0, O.BF16, O.BF16, True, True),      # on the border: sliced or whole, one launch either way
     (1000, 3000, 776, 0, O.BF16, O.BF16, True, True),       # tails in M, N and K
     (320, 1000, 200, 0, O.F16, O.F32, False, True),         # lhs M-contiguous, 4-byte output
     (128, 4096, 520, 0, O.BF16, O.BF16, True, False),       # rhs K-contiguous, 8 columns in the last tile
@@ -108,7 +109,7 @@ import numpy as np, torch
 from hodu_b200 import kernels as K
 from hodu_b200.layout import Layout
 from hodu_b200.op_metadatas import dot_metadata
-for (m, k, n) in [(512, 2048, 512), (1536, 1536, 1536), (128, 4096, 4096)]:
+for (m, k, n) in [(512, 2048, 512), (1024, 4096, 1024), (128, 4096, 4096)]:
     a = (torch.randn(m, k, device="cuda") / 8).bfloat16(); b = (torch.randn(k, n, device="cuda") / 8).bfloat16()
     c = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
     md = dot_metadata(Layout.from_shape((m, k)), Layout.from_shape((k, n)))
