@@ -157,9 +157,15 @@ struct ConvTail {
 };
 
 template <int BN> struct ConvCfg {
-  static constexpr uint32_t kStageA = 128u * 128u;   // 128 pixels x 64 channels
-  static constexpr uint32_t kStageB = BN * 128u;     // BN output channels x 64 k
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  // k-blocks (one filter tap x 64 channels) per stage: the narrow tiles take two, because the
+  // handshake of a stage (a wait, a commit, a producer iteration: ~250 cycles each for the one
+  // thread that runs it) costs more than the 128 or 256 MMA cycles of one of their k-blocks.
+  static constexpr uint32_t kKbPerStage = BN <= 128 ? 2u : 1u;
+  static constexpr uint32_t kStageA1 = 128u * 128u;   // 128 pixels x 64 channels
+  static constexpr uint32_t kStageB1 = BN * 128u;     // BN output channels x 64 k
+  static constexpr uint32_t kStageA = kKbPerStage * kStageA1;
+  static constexpr uint32_t kStageB = kKbPerStage * kStageB1;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 3 : 4);
   static constexpr size_t kSmem = kStages * (kStageA + kStageB) + 256 + 1024;
 };
 
@@ -223,8 +229,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_co
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer (a second producer
-    // thread for the weights measured no gain: the TMA unit, which takes a 128-byte row every few
-    // cycles, sets the pace, not the issuing thread)
+    // thread for the weights measured no gain)
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
@@ -234,19 +239,27 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_co
         const uint32_t img = p0 / p.n_img, r = p0 - img * p.n_img;
         const uint32_t oh0 = r / p.ow, ow0 = r - oh0 * p.ow;
         const int32_t base_w = static_cast<int32_t>(ow0) * p.sw - p.pw, base_h = static_cast<int32_t>(oh0) * p.sh - p.ph;
-        for (uint32_t tap = 0; ok && tap < taps; ++tap) {
-          const uint32_t fh = tap / p.kw, fw = tap - fh * p.kw;
-          for (uint32_t cb = 0; cb < p.c_blocks; ++cb) {
-            ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code_base | 1u);
-            if (!ok) break;
-            const uint32_t bar = smem_u32(&tail->full[s]);
-            mbar_arrive_expect_tx_relaxed(bar, Cfg::kStageA + Cfg::kStageB);
-            tma_load_im2col_4d(smem_a + s * Cfg::kStageA, &map_in, bar, static_cast<int32_t>(cb * 64u), base_w, base_h,
-                               static_cast<int32_t>(img), static_cast<uint16_t>(fw * p.dw), static_cast<uint16_t>(fh * p.dh));
-            tma_load_2d(smem_b + s * Cfg::kStageB, &map_w, bar, static_cast<int32_t>((tap * p.c_blocks + cb) * 64u),
+        // k-block kb = (tap, 64-channel block cb), taps outermost; fh, fw: the tap's row and column
+        uint32_t cb = 0, fh = 0, fw = 0;
+        for (uint32_t kb = 0; kb < k_blocks; kb += Cfg::kKbPerStage) {
+          ok = wait_bounded(smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag, p.status, code_base | 1u);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&tail->full[s]);
+          const uint32_t n_kb = Cfg::kKbPerStage == 1u ? 1u : min(Cfg::kKbPerStage, k_blocks - kb);
+          mbar_arrive_expect_tx_relaxed(bar, n_kb * (Cfg::kStageA1 + Cfg::kStageB1));
+#pragma unroll
+          for (uint32_t j = 0; j < Cfg::kKbPerStage; ++j) {
+            if (j >= n_kb) break;
+            tma_load_im2col_4d(smem_a + s * Cfg::kStageA + j * Cfg::kStageA1, &map_in, bar, static_cast<int32_t>(cb * 64u), base_w,
+                               base_h, static_cast<int32_t>(img), static_cast<uint16_t>(fw * p.dw), static_cast<uint16_t>(fh * p.dh));
+            tma_load_2d(smem_b + s * Cfg::kStageB + j * Cfg::kStageB1, &map_w, bar, static_cast<int32_t>((kb + j) * 64u),
                         static_cast<int32_t>(nt * BN));
-            if (++s == kStages) { s = 0; ph ^= 1u; }
+            if (++cb == p.c_blocks) {
+              cb = 0;
+              if (++fw == p.kw) { fw = 0; ++fh; }
+            }
           }
+          if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
     }
@@ -262,14 +275,19 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_co
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        for (uint32_t kb = 0; kb < k_blocks; kb += Cfg::kKbPerStage) {
           ok = wait_bounded(smem_u32(&tail->full[s]), ph, abort_flag, p.status, code_base | 3u);
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t a_desc = kmajor_desc128(smem_a + s * Cfg::kStageA), b_desc = kmajor_desc128(smem_b + s * Cfg::kStageB);
 #pragma unroll
-          for (uint32_t kk = 0; kk < 4; ++kk)     // 16 k per MMA = 32 bytes = 2 sixteen-byte units
-            umma<KIND_F16, 1>(d_tmem, a_desc + kk * 2u, b_desc + kk * 2u, p.idesc, (kb | kk) != 0u ? 1u : 0u);
+          for (uint32_t j = 0; j < Cfg::kKbPerStage; ++j) {
+            if (kb + j >= k_blocks) break;
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk)     // 16 k per MMA = 32 bytes = 2 sixteen-byte units
+              umma<KIND_F16, 1>(d_tmem, a_desc + j * (Cfg::kStageA1 >> 4) + kk * 2u, b_desc + j * (Cfg::kStageB1 >> 4) + kk * 2u, p.idesc,
+                                (kb | j | kk) != 0u ? 1u : 0u);
+          }
           umma_commit_1cta(smem_u32(&tail->empty[s]));
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
