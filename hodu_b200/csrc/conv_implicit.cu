@@ -160,12 +160,12 @@ template <int BN> struct ConvCfg {
   // k-blocks (one filter tap x 64 channels) per stage: the narrow tiles take two, because the
   // handshake of a stage (a wait, a commit, a producer iteration: ~250 cycles each for the one
   // thread that runs it) costs more than the 128 or 256 MMA cycles of one of their k-blocks.
-  static constexpr uint32_t kKbPerStage = BN <= 128 ? 2u : 1u;
+  static constexpr uint32_t kKbPerStage = BN == 64 ? 3u : (BN == 128 ? 2u : 1u);
   static constexpr uint32_t kStageA1 = 128u * 128u;   // 128 pixels x 64 channels
   static constexpr uint32_t kStageB1 = BN * 128u;     // BN output channels x 64 k
   static constexpr uint32_t kStageA = kKbPerStage * kStageA1;
   static constexpr uint32_t kStageB = kKbPerStage * kStageB1;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 3 : 4);
+  static constexpr int kStages = BN == 256 ? 4 : 3;
   static constexpr size_t kSmem = kStages * (kStageA + kStageB) + 256 + 1024;
 };
 
