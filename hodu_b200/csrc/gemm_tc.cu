@@ -90,12 +90,12 @@ template <int BN, bool PAIR, int MH> struct TileCfg {
   // mbarrier probe answers after ~200 cycles even when the phase is long complete), which is more
   // than the 128 or 256 MMA cycles of a k-block of the narrow one-CTA tiles: those stage two
   // k-blocks at a time and pay the handshake once for both.
-  static constexpr int kKbPerStage = (!PAIR && BN <= 128) ? 2 : 1;
+  static constexpr int kKbPerStage = ((!PAIR && BN <= 128) || (PAIR && MH == 1)) ? 2 : 1;
   static constexpr int kStageA1 = MH * kHalfA;                    // one k-block
   static constexpr int kStageB1 = PAIR ? 128 * 128 : BN * 128;
   static constexpr int kStageA = kKbPerStage * kStageA1;
   static constexpr int kStageB = kKbPerStage * kStageB1;
-  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 6) : (BN == 256 ? 4 : (BN == 128 ? 3 : 4));
+  static constexpr int kStages = PAIR ? (MH == 2 ? 4 : 3) : (BN == 256 ? 4 : (BN == 128 ? 3 : 4));
   static constexpr int kEpiWarps = 4 * MH * (MH == 2 ? 2 : 1);
   static constexpr int kEpiStage = 2048;  // per epilogue warp: a 32-row x 64-byte block
   static constexpr int kTmemCols = 2 * BN;  // two accumulators: double buffer (MH 1) or the two halves (MH 2)
@@ -409,7 +409,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
       const uint32_t bar = full0 + s * 8u;
       const uint32_t n_kb = kKbPerStage == 1u ? 1u : min(kKbPerStage, kb_hi - kb);   // k-blocks this stage holds
       if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes * n_kb);
-      else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes);
+      else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes * n_kb);
 #pragma unroll
       for (uint32_t j = 0; j < kKbPerStage; ++j) {
       if (j >= n_kb) break;
