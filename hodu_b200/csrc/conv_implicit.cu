@@ -447,7 +447,20 @@ int run_conv2d_implicit(int dtype, const void* input, const void* weight, void* 
     else count_launch();
   }
   if (r == 0) {
-    const int bn = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
+    // Output channels per tile: the widest tile the layer can fill, unless a narrower one puts the
+    // layer's tiles on more of the SMs (a 7x7x512 layer of batch 32 is 13 pixel tiles: 26 CTAs at 256
+    // channels, 104 at 64).  Estimate = waves x relative time of a k-block (1 : 1.15 : 1.5, measured).
+    int bn = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
+    {
+      const double tiles_m_d = static_cast<double>((pixels + 127) / 128);
+      double best = 1e300;
+      for (int c = bn; c >= 64; c /= 2) {
+        const double tiles = tiles_m_d * static_cast<double>((cout + c - 1) / c);
+        const double waves = tiles > st->sm_count ? tiles / st->sm_count : 1.0;
+        const double cost = waves * (c == 256 ? 1.5 : (c == 128 ? 1.15 : 1.0));
+        if (cost < best * 0.97) { best = cost; bn = c; }   // a narrower tile has to win by 3 %
+      }
+    }
     CUtensorMap mi, mw;
     {
       cuuint64_t dims[4] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
