@@ -45,7 +45,10 @@ CASES = [
     (1, 2, 3, (5, 5), (3, 3), (1, 1), (0, 0), (1, 1), O.BF16),          # tiny: generic kernel
     # in_channels a multiple of 64, bf16 / f16: the implicit form (no unfolded copy)
     (3, 128, 96, (17, 13), (3, 3), (2, 1), (1, 2), (1, 2), O.F16),      # tiles straddle images, odd extents, stride, dilation, ragged Cout
-    (2, 64, 256, (20, 24), (5, 5), (1, 1), (2, 2), (1, 1), O.BF16),     # 5x5, 256-wide channel tiles
+    (2, 64, 256, (20, 24), (5, 5), (1, 1), (2, 2), (1, 1), O.BF16),     # 5x5; few pixel tiles: 64-wide channel tiles, four per pixel tile
+    (8, 64, 256, (56, 56), (3, 3), (1, 1), (1, 1), (1, 1), O.BF16),     # 196 pixel tiles: 256-wide channel tiles
+    (16, 64, 128, (28, 28), (3, 3), (1, 1), (1, 1), (1, 1), O.F16),     # 98 pixel tiles: 128-wide channel tiles (two k-blocks per stage)
+    (4, 512, 512, (7, 7), (3, 3), (1, 1), (1, 1), (1, 1), O.BF16),      # deep layer: 2 pixel tiles x 8 channel tiles, 72 k-blocks
     (40, 64, 64, (9, 9), (3, 3), (1, 1), (0, 0), (1, 1), O.BF16),       # no padding; 1960 pixels: a ragged last tile
     (2, 192, 64, (31, 31), (3, 3), (3, 3), (1, 1), (1, 1), O.F16),      # three channel blocks, stride 3
 ]
