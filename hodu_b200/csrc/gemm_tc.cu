@@ -132,7 +132,7 @@ struct TcParams {
   uint32_t k_gen_limit;   // generations of k_gen blocks up to here, then ONE generation for the rest
   uint32_t bdim1, bdim2;  // batch = (b0 * bdim1 + b1) * bdim2 + b2
   uint32_t bk;            // K elements per stage (128 bytes worth)
-  uint32_t k_splits;      // CTAs (or CTA pairs) of a cluster that share one tile, each taking a slice of K
+  uint32_t k_splits;      // CTAs of a cluster that share one tile, each taking a slice of K (1: no cluster)
   uint32_t kb_per_split;  // k-blocks per slice (the last slice takes what is left)
   OperandLoad a, b;
   uint32_t idesc;
@@ -411,10 +411,10 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const OperandLo
       if (!PAIR) mbar_arrive_expect_tx_relaxed(bar, my_bytes * n_kb);
       else if (rank == 0) mbar_arrive_expect_tx_relaxed(smem_u32(&tail->full[s]), 2u * my_bytes * n_kb);
 #pragma unroll
-      for (uint32_t j = 0; j < kKbPerStage; ++j) {
-      if (j >= n_kb) break;
-      const int32_t k0 = static_cast<int32_t>((kb + j) * p.bk);
-      uint32_t dst = smem_operand + s * kStageBytes + j * kKbBytes;
+      for (uint32_t h = 0; h < kKbPerStage; ++h) {   // the k-blocks of this stage
+      if (h >= n_kb) break;
+      const int32_t k0 = static_cast<int32_t>((kb + h) * p.bk);
+      uint32_t dst = smem_operand + s * kStageBytes + h * kKbBytes;
       for (uint32_t i = 0; i < o.boxes; ++i, dst += o.box_bytes) {
         const CUtensorMap* mp = map0;
         uint32_t j = i;
@@ -784,7 +784,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if constexpr (kSplitCapable) split_tile = k_splits > 1u;
       if (split_tile) {
         if constexpr (kSplitCapable) {
-          // K slices of one tile in the CTAs (or pairs) of this cluster: see the kernel's header.
+          // K slices of one tile in the CTAs of this cluster: see the kernel's header.
           static_assert(kChunks * 16384u <= static_cast<uint32_t>(kStages * (kStageA + kStageB)),
                         "the partial sums of a tile must fit the operand ring");
           const uint32_t per = kChunks / k_splits;             // chunks each slice owns
@@ -1318,7 +1318,8 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     const char* bad = nullptr;
     if (p.a.boxes * p.a.box_bytes != static_cast<uint32_t>(Cfg::kStageA1)) bad = "lhs boxes do not fill a k-block of a stage";
     else if (p.b.boxes * p.b.box_bytes != static_cast<uint32_t>(Cfg::kStageB1)) bad = "rhs boxes do not fill a k-block of a stage";
-    else if (Cfg::kKbPerStage == 2 && KIND == KIND_TF32 && ((p.k_gen & 1u) || (p.k_gen_limit & 1u)) && p.k_gen < p.k_blocks)
+    else if (Cfg::kKbPerStage == 2 && KIND == KIND_TF32 && p.k_gen < p.k_blocks &&
+             ((p.k_gen & 1u) || (p.k_gen_limit < p.k_blocks && (p.k_gen_limit & 1u))))
       bad = "accumulator generations must start at even k-blocks when a stage holds two";
     else if (Cfg::kTmemCols > 512 || (Cfg::kTmemCols & (Cfg::kTmemCols - 1)) != 0) bad = "TMEM columns not a power of two <= 512";
     else if (static_cast<uint64_t>(p.tiles_m) * kTileRows < p.M || static_cast<uint64_t>(p.tiles_m - 1) * kTileRows >= p.M)
@@ -1446,9 +1447,10 @@ int launch_gemm_tc_planned(const Problem& pb, DeviceState* st, cudaStream_t stre
   //   form 1: CTA pair, 256 x 256 tile, double-buffered accumulator
   //   form 0: one CTA, 128 x BN tile; an 8-bit N-contiguous rhs needs BN >= 128 (one 128-byte
   //           swizzle row holds 128 of its elements)
-  // Cycles per k-block = max(MMA cycles, operand bytes one SM takes in / ~50 B per cycle): the
-  // measured tensor-pipe utilisations (512x256: 0.9, 256x256: 0.78, 128x256: 0.53) follow the
-  // bytes per MMA cycle each form needs (48, 64, 96 B/clk), not DRAM or L2 bandwidth.
+  // Cycles per k-block = max(MMA cycles, operand bytes one SM takes in / ~50 B per cycle): a fit
+  // to the measured tensor-pipe utilisations of large products (512x256: 0.9, 256x256: 0.78,
+  // 128x256: 0.53), which follow the bytes per MMA cycle each form needs (48, 64, 96 B/clk).
+  // (Launches of few tiles are judged by a second estimate further down.)
   const int forced = forced_path();
   const int units_pair = st->sm_count / 2 > 0 ? st->sm_count / 2 : 1;
   const double k_blocks_d = static_cast<double>((pb.K + (128 / esize) - 1) / (128 / esize));
