@@ -1303,7 +1303,9 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     max_ctas[device][split_log2].store(resident, std::memory_order_relaxed);
     if (!PAIR) g_split_capacity[device][split_log2].store(resident, std::memory_order_relaxed);
   }
-  // K slices meet at a cluster barrier, so every tile's cluster has to be resident at once.
+  // K slices are planned for ONE wave of clusters (the hardware keeps the CTAs of a cluster
+  // together, so more tiles than resident clusters would still be correct, but they would run
+  // in waves, which is what slicing is there to avoid): such a plan goes back to the planner.
   if (p.k_splits > 1u && p.num_tiles > static_cast<uint32_t>(resident)) return kSplitDoesNotFit;
   const int units = static_cast<int>(p.num_tiles < static_cast<uint32_t>(resident) ? p.num_tiles : resident);
   cfg.gridDim = dim3(cluster_ctas * static_cast<unsigned>(units), 1, 1);
@@ -1517,7 +1519,7 @@ int launch_gemm_tc_planned(const Problem& pb, DeviceState* st, cudaStream_t stre
           const int64_t tiles = ((pb.M + 127) / 128) * ((pb.N + c - 1) / c) * pb.batches;
           const int measured = g_split_capacity[device][ks == 8 ? 3 : (ks == 4 ? 2 : 1)].load(std::memory_order_relaxed);
           const int64_t capacity = measured > 0 ? measured : st->sm_count / ks;
-          if (tiles > capacity || k_blocks_d < 4.0 * ks) continue;   // all clusters resident; >= 4 k-blocks a slice
+          if (tiles > capacity || k_blocks_d < 4.0 * ks) continue;   // one wave of clusters; >= 4 k-blocks a slice
           const int chunks = c / 32, per = chunks / ks;
           const double t = 5200.0 + static_cast<double>((static_cast<int64_t>(k_blocks_d) + ks - 1) / ks) * kblock_fit(0, c) +
                            (chunks - per) * 285.0 + 700.0 + per * (chunk_clk + (ks - 1) * 700.0);
