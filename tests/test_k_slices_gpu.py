@@ -73,6 +73,42 @@ def test_k_slices_match_oracle(case):
         check_close(got, want, out_dt, tol)
 
 
+def _random_cases(n_cases, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    while len(out) < n_cases:
+        m = int(rng.choice([64, 128, 200, 256, 384, 500, 512, 768, 1000]))
+        n = int(rng.choice([64, 128, 192, 256, 320, 512, 776, 1024, 1536]))
+        k = int(rng.choice([512, 1000, 1024, 2048, 3000, 4096, 6144]))
+        a_kmajor, b_nmajor = bool(rng.integers(2)), bool(rng.integers(2))
+        dt = int(rng.choice([O.BF16, O.F16]))
+        # TMA takes the operand as it lies only when the pitch of its contiguous index is a multiple of 16 bytes
+        if ((m if not a_kmajor else k) * 2) % 16 or ((n if b_nmajor else k) * 2) % 16:
+            continue
+        out.append((m, k, n, dt, a_kmajor, b_nmajor))
+    return out
+
+
+RANDOM = _random_cases(24, 20241)
+
+
+@pytest.mark.parametrize("case", RANDOM, ids=[f"{c[0]}x{c[1]}x{c[2]}-{DType(c[3])}-{int(c[4])}{int(c[5])}" for c in RANDOM])
+def test_random_products_with_few_tiles(case):
+    """Fixed-seed sweep over shapes with few output tiles (most run with 2, 4 or 8 K slices) and all
+    four layout combinations: one launch each, oracle parity."""
+    m, k, n, dt, a_kmajor, b_nmajor = case
+    rng = np.random.default_rng(m + 3 * k + 5 * n)
+    a = rand_storage(rng, dt, (m, k) if a_kmajor else (k, m))
+    b = rand_storage(rng, dt, (k, n) if b_nmajor else (n, k))
+    la = Layout.from_shape((m, k)) if a_kmajor else Layout.from_shape((k, m)).transpose(0, 1)
+    lb = Layout.from_shape((k, n)) if b_nmajor else Layout.from_shape((n, k)).transpose(0, 1)
+    md = dot_metadata(la, lb)
+    before = K.launch_count()
+    got, taken = gpu_matmul(a, b, md, dt, dt, is_dot=True)
+    assert K.launch_count() - before == 1 and taken == K._lib.PATH_TENSOR
+    check_close(got, O.matmul(a, b, md, dt, dt, 1.0, is_dot=True), dt, 1e-2)
+
+
 @pytest.mark.parametrize("flags", [K._lib.LINEAR_ROUND_EACH_OP, K._lib.LINEAR_ROUND_ONCE], ids=["each_op", "once"])
 def test_k_slices_with_bias(flags):
     """hodu_nn::Linear on few tokens: the bias is added once, by the slice that stores the chunk."""
